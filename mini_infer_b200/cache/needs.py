@@ -54,16 +54,18 @@ class PagedCacheNeed:
 
 @dataclass(frozen=True)
 class KVNeed(PagedCacheNeed):
-    """Keys and values per token: ``k`` and ``v`` pages of ``[num_kv_heads, page_size, head_dim]``."""
+    """Keys and values per token: ``k`` pages of ``[num_kv_heads, page_size, head_dim]`` and ``v`` pages of
+    ``[num_kv_heads, page_size, value_dim]`` (``value_dim`` 0: as ``head_dim``)."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
     pages_fraction: float = 1.0
+    value_dim: int = 0
 
     def tensors(self, page_size: int) -> List[PageTensor]:
-        shape = (self.num_kv_heads, page_size, self.head_dim)
-        return [("k", shape, None), ("v", shape, None)]
+        return [("k", (self.num_kv_heads, page_size, self.head_dim), None),
+                ("v", (self.num_kv_heads, page_size, self.value_dim or self.head_dim), None)]
 
 
 @dataclass(frozen=True)

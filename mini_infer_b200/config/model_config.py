@@ -316,7 +316,11 @@ def read_config_json(path_or_folder: str) -> Dict[str, Any]:
 
 
 def architecture_name(j: Dict[str, Any]) -> str:
+    """The name the model registry is asked for: ``architectures[0]``, or the string under ``architecture``."""
     archs = j.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json has no 'architectures' entry naming the model class")
-    return archs[0]
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    one = j.get("architecture")
+    if isinstance(one, str) and one:
+        return one
+    raise ConfigError("config.json has no 'architectures' (or 'architecture') entry naming the model class")

@@ -97,10 +97,13 @@ def prenorm_layer(name: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.  ``cache_from`` names an earlier schedule position
-    whose caches this run reads, role by role (it then writes none of its own)."""
+    whose caches this run reads, role by role (it then writes none of its own).
+    ``args`` is handed to the layer's block for this run (``ctx.entry_args``): a layer
+    that runs several times may need to know which run it is."""
 
     layer: int
     cache_from: Optional[int] = None
+    args: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

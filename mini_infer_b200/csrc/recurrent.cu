@@ -1,0 +1,380 @@
+// Mixers that carry a fixed-size state per request instead of a cache that grows:
+//
+//   causal_conv_silu   short causal convolution over time per channel (+ bias) and silu, with the last
+//                      taps-1 inputs of a request kept in its state slot between steps
+//   delta_scan         gated delta rule with one decay per head and key channel:
+//                        S <- diag(g_t) S ;  u = beta_t (v_t - S^T k_t) ;  S <- S + k_t u^T ;  o_t = S^T q_t
+//   ssd_scan           selective state-space recurrence with a scalar decay per head (Mamba-2):
+//                        S <- exp(-A dt_t) S + dt_t B_t x_t^T ;  y_t = S^T C_t + D x_t
+//   gated_group_rmsnorm  RMS norm over equal groups of a row, with a gate before (silu) or after (sigmoid) it
+//
+// The recurrences walk a request's tokens of the step in order, one block per (request, head, slice of
+// 32 value columns); a thread holds a quarter of one column of S in registers, so that the products with
+// k_t and q_t (or C_t) are sums inside a thread and over four neighbouring lanes.  What a token needs
+// besides S (unit vectors, decays, step sizes) is prepared for 8 tokens at a time by the whole block.
+// All arithmetic is float, whatever the storage type of the activations; the state is float.  The order
+// of the additions of a token depends on nothing but the sizes of the model, so a prompt cut into
+// portions, decoded token by token or batched with others gives the same bits.
+//
+// State slots: state[slot * state_stride + offset ...]; rows of a step that belong to no request carry a
+// spare slot of their own.
+
+#include "common.cuh"
+
+namespace mi {
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+// log(1 + e^x) without overflow; equal to x in float beyond 20
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+constexpr int kMaxTaps = 8;
+
+// ---------------------------------------------------------------------------
+// out[t, c] = silu(bias[c] + sum_j w[c, j] * in(t - (taps-1-j), c)), inputs before the step's first token
+// come from the request's state (time-major: state[j * C + c] is the input at local position
+// j - (taps-1)), zeros for a fresh request because a new slot is zeroed.
+// ---------------------------------------------------------------------------
+template <typename WT>
+__global__ void __launch_bounds__(256)
+causal_conv_silu_kernel(const float* __restrict__ x, int ldx, const WT* __restrict__ w, const WT* __restrict__ bias,
+                        const float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
+                        const int* __restrict__ req_of_token, const int* __restrict__ state_slot,
+                        float* __restrict__ out, int ld_out, int C, int taps, int T) {
+    wait_for_earlier_kernels();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float wt[kMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) wt[j] = j < taps ? to_float(w[(int64_t)c * taps + j]) : 0.f;
+    const float bv = bias ? to_float(bias[c]) : 0.f;
+    for (int t = blockIdx.y; t < T; t += gridDim.y) {
+        const int b = req_of_token[t];
+        const int i = t - q_start[b];
+        const float* st = state + (int64_t)state_slot[b] * state_stride;
+        float acc = bv;
+#pragma unroll
+        for (int j = 0; j < kMaxTaps; ++j) {
+            if (j < taps) {
+                const int s = i - (taps - 1 - j);      // local position of the input of tap j
+                const float v = s >= 0 ? x[(int64_t)(t - (taps - 1 - j)) * ldx + c] : st[(int64_t)(s + taps - 1) * C + c];
+                acc += wt[j] * v;
+            }
+        }
+        out[(int64_t)t * ld_out + c] = silu_f(acc);
+    }
+}
+
+// The last taps-1 inputs of every request after this step; one thread per (request, channel) moves its
+// entries in ascending order, so an entry is read before it is overwritten.
+__global__ void __launch_bounds__(256)
+conv_state_update_kernel(const float* __restrict__ x, int ldx, float* __restrict__ state, int64_t state_stride,
+                         const int* __restrict__ q_start, const int* __restrict__ state_slot, int C, int taps) {
+    wait_for_earlier_kernels();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= C) return;
+    const int q0 = q_start[b], n = q_start[b + 1] - q0;
+    float* st = state + (int64_t)state_slot[b] * state_stride;
+    for (int j = 0; j < taps - 1; ++j) {
+        const int s = n + j - (taps - 1);              // local position that becomes entry j
+        st[(int64_t)j * C + c] = s >= 0 ? x[(int64_t)(q0 + s) * ldx + c] : st[(int64_t)(n + j) * C + c];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The two recurrences.  Block = 128 threads = 32 value columns x 4 lanes; lane r of a column holds the
+// rows r, r+4, r+8, ... of that column (RP of them).  Tokens are prepared 8 at a time.
+// ---------------------------------------------------------------------------
+constexpr int kScanCols = 32;
+constexpr int kScanLanes = 4;
+constexpr int kScanChunk = 8;
+
+__device__ __forceinline__ float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+// qkv: [T, ld_qkv] float, q heads at column 0 (G x d), k heads at G*d, v heads at 2*G*d (H x dv), all after
+// the convolution; beta_raw: [T, ld_beta] at its own pointer (H columns); a_raw: [T, ld_a] (H x d columns,
+// before dt_bias and softplus).  out: [T, H*dv] float.
+template <int RP>
+__global__ void __launch_bounds__(kScanCols * kScanLanes)
+delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __restrict__ beta_raw, int ld_beta,
+                  const float* __restrict__ a_raw, int ld_a, const float* __restrict__ a_log,
+                  const float* __restrict__ dt_bias, float* __restrict__ state, int64_t state_stride,
+                  const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ out,
+                  int H, int G, int d, int dv, float q_scale) {
+    extern __shared__ float sm[];
+    constexpr int DP = RP * kScanLanes;                 // rows, padded
+    float* qs = sm;                                     // [chunk][DP] unit q times q_scale
+    float* ks = qs + kScanChunk * DP;                   // [chunk][DP] unit k
+    float* gs = ks + kScanChunk * DP;                   // [chunk][DP] decay
+    float* vs = gs + kScanChunk * DP;                   // [chunk][32] v of this slice
+    float* bs = vs + kScanChunk * kScanCols;            // [chunk] beta
+    wait_for_earlier_kernels();
+    const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * kScanCols;
+    const int hk = h / (H / G);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = tid & (kScanLanes - 1), col = col0 + (tid >> 2);
+    const bool col_ok = col < dv;
+    const int q0 = q_start[b], n = q_start[b + 1] - q0;
+    float* S = state + (int64_t)state_slot[b] * state_stride + (int64_t)h * d * dv;
+    float s[RP];
+#pragma unroll
+    for (int m = 0; m < RP; ++m) {
+        const int i = r + kScanLanes * m;
+        s[m] = (col_ok && i < d) ? S[(int64_t)i * dv + col] : 0.f;
+    }
+    const float neg_a = -expf(a_log[h]);
+    for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+        const int nc = min(kScanChunk, n - c0);
+        __syncthreads();                                // the chunk before has been consumed
+        // a warp prepares tokens warp, warp + 4 of the chunk
+        for (int tt = warp; tt < nc; tt += 4) {
+            const int64_t t = q0 + c0 + tt;
+            const float* qrow = qkv + t * ld_qkv + (int64_t)hk * d;
+            const float* krow = qkv + t * ld_qkv + (int64_t)(G + hk) * d;
+            float qq = 0.f, kk = 0.f;
+            for (int i = lane; i < d; i += 32) { const float a = qrow[i], c = krow[i]; qq += a * a; kk += c * c; }
+            qq = warp_sum(qq);
+            kk = warp_sum(kk);
+            const float qn = q_scale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
+            const float* arow = a_raw + t * ld_a + (int64_t)h * d;
+            for (int i = lane; i < DP; i += 32) {
+                float qv = 0.f, kv = 0.f, gv = 1.f;
+                if (i < d) {
+                    qv = qrow[i] * qn;
+                    kv = krow[i] * kn;
+                    gv = expf(neg_a * softplus_f(arow[i] + dt_bias[(int64_t)h * d + i]));
+                }
+                qs[tt * DP + i] = qv; ks[tt * DP + i] = kv; gs[tt * DP + i] = gv;
+            }
+            const int cc = col0 + lane;
+            vs[tt * kScanCols + lane] = cc < dv ? qkv[t * ld_qkv + (int64_t)2 * G * d + (int64_t)h * dv + cc] : 0.f;
+            if (lane == 0) bs[tt] = sigmoid_f(beta_raw[t * ld_beta + h]);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nc; ++tt) {
+            const float* kq = ks + tt * DP;
+            const float* gq = gs + tt * DP;
+            const float* qq = qs + tt * DP;
+            float acc = 0.f;
+#pragma unroll
+            for (int m = 0; m < RP; ++m) {
+                const int i = r + kScanLanes * m;
+                s[m] *= gq[i];
+                acc += s[m] * kq[i];
+            }
+            acc = quad_sum(acc);
+            const float u = bs[tt] * (vs[tt * kScanCols + (tid >> 2)] - acc);
+            float o = 0.f;
+#pragma unroll
+            for (int m = 0; m < RP; ++m) {
+                const int i = r + kScanLanes * m;
+                s[m] += kq[i] * u;
+                o += s[m] * qq[i];
+            }
+            o = quad_sum(o);
+            if (r == 0 && col_ok) out[(int64_t)(q0 + c0 + tt) * H * dv + (int64_t)h * dv + col] = o;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < RP; ++m) {
+        const int i = r + kScanLanes * m;
+        if (col_ok && i < d) S[(int64_t)i * dv + col] = s[m];
+    }
+}
+
+// xbc: [T, ld_x] float after the convolution: x heads at column 0 (H x P), B groups at H*P (G x N), C groups
+// at H*P + G*N; dt_raw: [T, ld_dt] (H columns, before dt_bias and softplus).  out: [T, H*P] float.
+template <int RP>
+__global__ void __launch_bounds__(kScanCols * kScanLanes)
+ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict__ dt_raw, int ld_dt,
+                const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
+                const int* __restrict__ state_slot, float* __restrict__ out, int H, int G, int N, int P) {
+    extern __shared__ float sm[];
+    constexpr int NP = RP * kScanLanes;
+    float* Bs = sm;                                     // [chunk][NP] dt * B
+    float* Cs = Bs + kScanChunk * NP;                   // [chunk][NP]
+    float* xs = Cs + kScanChunk * NP;                   // [chunk][32]
+    float* as = xs + kScanChunk * kScanCols;            // [chunk] decay
+    wait_for_earlier_kernels();
+    const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * kScanCols;
+    const int g = h / (H / G);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r = tid & (kScanLanes - 1), col = col0 + (tid >> 2);
+    const bool col_ok = col < P;
+    const int q0 = q_start[b], n = q_start[b + 1] - q0;
+    float* S = state + (int64_t)state_slot[b] * state_stride + (int64_t)h * N * P;
+    float s[RP];
+#pragma unroll
+    for (int m = 0; m < RP; ++m) {
+        const int i = r + kScanLanes * m;
+        s[m] = (col_ok && i < N) ? S[(int64_t)i * P + col] : 0.f;
+    }
+    const float neg_a = -expf(a_log[h]);
+    const float dskip = d_skip[h];
+    const float bias = dt_bias[h];
+    for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+        const int nc = min(kScanChunk, n - c0);
+        __syncthreads();
+        for (int tt = warp; tt < nc; tt += 4) {
+            const int64_t t = q0 + c0 + tt;
+            const float dt = softplus_f(dt_raw[t * ld_dt + h] + bias);
+            const float* brow = xbc + t * ld_x + (int64_t)H * P + (int64_t)g * N;
+            const float* crow = brow + (int64_t)G * N;
+            for (int i = lane; i < NP; i += 32) {
+                Bs[tt * NP + i] = i < N ? dt * brow[i] : 0.f;
+                Cs[tt * NP + i] = i < N ? crow[i] : 0.f;
+            }
+            const int cc = col0 + lane;
+            xs[tt * kScanCols + lane] = cc < P ? xbc[t * ld_x + (int64_t)h * P + cc] : 0.f;
+            if (lane == 0) as[tt] = expf(neg_a * dt);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nc; ++tt) {
+            const float* Bq = Bs + tt * NP;
+            const float* Cq = Cs + tt * NP;
+            const float a = as[tt], xv = xs[tt * kScanCols + (tid >> 2)];
+            float y = 0.f;
+#pragma unroll
+            for (int m = 0; m < RP; ++m) {
+                const int i = r + kScanLanes * m;
+                s[m] = a * s[m] + Bq[i] * xv;
+                y += s[m] * Cq[i];
+            }
+            y = quad_sum(y);
+            if (r == 0 && col_ok) out[(int64_t)(q0 + c0 + tt) * H * P + (int64_t)h * P + col] = y + dskip * xv;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < RP; ++m) {
+        const int i = r + kScanLanes * m;
+        if (col_ok && i < N) S[(int64_t)i * P + col] = s[m];
+    }
+}
+
+// ---------------------------------------------------------------------------
+// One block per (token, group of `gs` columns):
+//   mode 0:  z = y * silu(gate);  out = z * rsqrt(mean(z^2) + eps) * w        (gate before the norm)
+//   mode 1:  out = y * rsqrt(mean(y^2) + eps) * w * sigmoid(gate)             (gate after the norm)
+// w has `wlen` entries and column c of the row uses w[c % wlen].
+// ---------------------------------------------------------------------------
+template <typename AT, typename WT>
+__global__ void __launch_bounds__(256)
+gated_group_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ gate, int ld_gate,
+                           const WT* __restrict__ w, int wlen, AT* __restrict__ out, int n, int gs, int mode,
+                           float eps) {
+    __shared__ float scratch[32];
+    wait_for_earlier_kernels();
+    const int t = blockIdx.x, c0 = blockIdx.y * gs;
+    const float* yr = y + (int64_t)t * n + c0;
+    const float* gr = gate + (int64_t)t * ld_gate + c0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        float v = yr[i];
+        if (mode == 0) v *= silu_f(gr[i]);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rr = 1.0f / sqrtf(ss / (float)gs + eps);
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        float v = yr[i];
+        if (mode == 0) v *= silu_f(gr[i]);
+        v = v * rr * to_float(w[(c0 + i) % wlen]);
+        if (mode == 1) v *= sigmoid_f(gr[i]);
+        out[(int64_t)t * n + c0 + i] = from_float<AT>(v);
+    }
+}
+
+}  // namespace mi
+
+using namespace mi;
+
+extern "C" {
+
+int mi_causal_conv_silu(const float* x, int ldx, const void* w, const void* bias, int wdtype, float* state,
+                        int64_t state_stride, const int* q_start, const int* req_of_token, const int* state_slot,
+                        float* out, int ld_out, int C, int taps, int T, int B, cudaStream_t stream) {
+    if (T <= 0 || C <= 0) return kOk;
+    if (taps < 1 || taps > kMaxTaps) {
+        set_last_error("causal convolution: %d taps are outside [1, %d]", taps, kMaxTaps);
+        return kBadShape;
+    }
+    if (B > 65535) { set_last_error("causal convolution: %d requests exceed the grid limit", B); return kBadShape; }
+    const int cb = (C + 255) / 256;
+    int ty = T < 4096 ? T : 4096;
+    MI_DISPATCH_1(wdtype, WT,
+        launch_dependent(causal_conv_silu_kernel<WT>, dim3(cb, ty), dim3(256), 0, stream, x, ldx, (const WT*)w,
+                         (const WT*)bias, (const float*)state, state_stride, q_start, req_of_token, state_slot, out,
+                         ld_out, C, taps, T));
+    int launched = 1;
+    if (taps > 1) {
+        launch_dependent(conv_state_update_kernel, dim3(cb, B), dim3(256), 0, stream, x, ldx, state, state_stride,
+                         q_start, state_slot, C, taps);
+        launched = 2;
+    }
+    return finish_launch("causal_conv_silu", launched);
+}
+
+#define MI_SCAN_DISPATCH(rows, ...)                                                     \
+    do {                                                                                \
+        if ((rows) <= 64) { constexpr int RP = 16; __VA_ARGS__; }                       \
+        else if ((rows) <= 128) { constexpr int RP = 32; __VA_ARGS__; }                 \
+        else { constexpr int RP = 64; __VA_ARGS__; }                                    \
+    } while (0)
+
+int mi_delta_scan(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
+                  const float* a_log, const float* dt_bias, float* state, int64_t state_stride, const int* q_start,
+                  const int* state_slot, float* out, int B, int H, int G, int d, int dv, float q_scale,
+                  cudaStream_t stream) {
+    if (B <= 0) return kOk;
+    if (d < 1 || d > 256 || dv < 1) { set_last_error("delta rule: key size %d outside [1, 256] or value size %d", d, dv); return kBadShape; }
+    if (G < 1 || H % G) { set_last_error("delta rule: %d heads are not a multiple of %d key heads", H, G); return kBadShape; }
+    if (B > 65535 || H > 65535) { set_last_error("delta rule: batch %d or heads %d exceed the grid limit", B, H); return kBadShape; }
+    const dim3 grid((dv + kScanCols - 1) / kScanCols, H, B);
+    MI_SCAN_DISPATCH(d, {
+        const size_t smem = sizeof(float) * (kScanChunk * (3 * RP * kScanLanes + kScanCols + 1));
+        launch_dependent(delta_scan_kernel<RP>, grid, dim3(kScanCols * kScanLanes), smem, stream, qkv, ld_qkv,
+                         beta_raw, ld_beta, a_raw, ld_a, a_log, dt_bias, state, state_stride, q_start, state_slot,
+                         out, H, G, d, dv, q_scale);
+    });
+    return finish_launch("delta_scan");
+}
+
+int mi_ssd_scan(const float* xbc, int ld_x, const float* dt_raw, int ld_dt, const float* dt_bias, const float* a_log,
+                const float* d_skip, float* state, int64_t state_stride, const int* q_start, const int* state_slot,
+                float* out, int B, int H, int G, int N, int P, cudaStream_t stream) {
+    if (B <= 0) return kOk;
+    if (N < 1 || N > 256 || P < 1) { set_last_error("state-space scan: state size %d outside [1, 256] or head size %d", N, P); return kBadShape; }
+    if (G < 1 || H % G) { set_last_error("state-space scan: %d heads are not a multiple of %d groups", H, G); return kBadShape; }
+    if (B > 65535 || H > 65535) { set_last_error("state-space scan: batch %d or heads %d exceed the grid limit", B, H); return kBadShape; }
+    const dim3 grid((P + kScanCols - 1) / kScanCols, H, B);
+    MI_SCAN_DISPATCH(N, {
+        const size_t smem = sizeof(float) * (kScanChunk * (2 * RP * kScanLanes + kScanCols + 1));
+        launch_dependent(ssd_scan_kernel<RP>, grid, dim3(kScanCols * kScanLanes), smem, stream, xbc, ld_x, dt_raw,
+                         ld_dt, dt_bias, a_log, d_skip, state, state_stride, q_start, state_slot, out, H, G, N, P);
+    });
+    return finish_launch("ssd_scan");
+}
+
+int mi_gated_group_rmsnorm(const float* y, const float* gate, int ld_gate, const void* w, int wdtype, int wlen,
+                           void* out, int adtype, int T, int n, int groups, int mode, float eps, cudaStream_t stream) {
+    if (T <= 0 || n <= 0) return kOk;
+    if (groups < 1 || n % groups || groups > 65535 || wlen < 1 || (mode != 0 && mode != 1)) {
+        set_last_error("gated group norm: %d columns in %d groups, weight of %d, mode %d", n, groups, wlen, mode);
+        return kBadShape;
+    }
+    const int gs = n / groups;
+    int threads = 32;
+    while (threads < gs && threads < 256) threads *= 2;
+    MI_DISPATCH_2(adtype, AT, wdtype, WT,
+        launch_dependent(gated_group_rmsnorm_kernel<AT, WT>, dim3(T, groups), dim3(threads), 0, stream, y, gate,
+                         ld_gate, (const WT*)w, wlen, (AT*)out, n, gs, mode, eps));
+    return finish_launch("gated_group_rmsnorm");
+}
+
+}  // extern "C"

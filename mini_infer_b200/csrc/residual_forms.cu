@@ -1,0 +1,140 @@
+// Row-wise kernels of residual arrangements other than "norm, part, add, norm, part, add":
+//
+//   add2_rmsnorm_scalar   hidden += a + b (both optional), then ONE root mean square per row and two
+//                         outputs that differ by a scalar gain only: the two norms of a block whose mixer
+//                         and feed-forward read the same residual, when each norm's weight is one number
+//   geglu_tanh            out = gelu_tanh(gate) * up, gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+//   concat_cast           out[t] = [hidden[t] + a[t] + b[t] | other[t]] in the activation type: the input
+//                         of a projection that reads the residual beside a second stream
+//   rows_plus_vec         hidden[t] = y[t] + vec: a projection's result becomes the residual, plus one row
+
+#include "common.cuh"
+
+namespace mi {
+
+template <typename AT>
+__global__ void __launch_bounds__(256)
+add2_rmsnorm_scalar_kernel(float* __restrict__ hidden, const float* __restrict__ a, const float* __restrict__ b,
+                           const int* __restrict__ rows, const float* __restrict__ gain1,
+                           const float* __restrict__ gain2, AT* __restrict__ out1, AT* __restrict__ out2, int H,
+                           float eps) {
+    __shared__ float scratch[32];
+    wait_for_earlier_kernels();
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* h = hidden + (int64_t)src * H;
+    const float* pa = a ? a + (int64_t)src * H : nullptr;
+    const float* pb = b ? b + (int64_t)src * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = h[i];
+        if (pa || pb) {
+            float dlt = pa ? pa[i] : 0.f;
+            if (pb) dlt += pb[i];
+            v += dlt;
+            if (!rows) h[i] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rr = 1.0f / sqrtf(ss / (float)H + eps);
+    const float g1 = gain1[0], g2 = gain2 ? gain2[0] : 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = h[i];
+        if (rows && (pa || pb)) {
+            float dlt = pa ? pa[i] : 0.f;
+            if (pb) dlt += pb[i];
+            v += dlt;
+        }
+        const float nv = v * rr;
+        out1[(int64_t)r * H + i] = from_float<AT>(nv * g1);
+        if (out2) out2[(int64_t)r * H + i] = from_float<AT>(nv * g2);
+    }
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename AT>
+__global__ void geglu_tanh_kernel(const AT* __restrict__ gu, AT* __restrict__ out, int64_t total, int I) {
+    wait_for_earlier_kernels();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        const float g = to_float(gu[t * 2 * I + i]);
+        const float u = to_float(gu[t * 2 * I + I + i]);
+        out[idx] = from_float<AT>(gelu_tanh_f(g) * u);
+    }
+}
+
+template <typename AT>
+__global__ void __launch_bounds__(256)
+concat_cast_kernel(const float* __restrict__ hidden, const float* __restrict__ a, const float* __restrict__ b,
+                   const float* __restrict__ other, AT* __restrict__ out, int H) {
+    wait_for_earlier_kernels();
+    const int64_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = hidden[t * H + i];
+        if (a || b) {
+            float dlt = a ? a[t * H + i] : 0.f;
+            if (b) dlt += b[t * H + i];
+            v += dlt;
+        }
+        out[t * 2 * H + i] = from_float<AT>(v);
+        out[t * 2 * H + H + i] = from_float<AT>(other[t * H + i]);
+    }
+}
+
+template <typename WT>
+__global__ void __launch_bounds__(256)
+rows_plus_vec_kernel(float* __restrict__ hidden, const float* __restrict__ y, const WT* __restrict__ vec, int H) {
+    wait_for_earlier_kernels();
+    const int64_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) hidden[t * H + i] = y[t * H + i] + to_float(vec[i]);
+}
+
+}  // namespace mi
+
+using namespace mi;
+
+extern "C" {
+
+int mi_add2_rmsnorm_scalar(float* hidden, const float* a, const float* b, const int* rows, const float* gain1,
+                           const float* gain2, void* out1, void* out2, int adtype, int n, int H, float eps,
+                           cudaStream_t stream) {
+    if (n <= 0 || H <= 0) return kOk;
+    MI_DISPATCH_1(adtype, AT,
+        launch_dependent(add2_rmsnorm_scalar_kernel<AT>, dim3(n), dim3(256), 0, stream, hidden, a, b, rows, gain1,
+                         gain2, (AT*)out1, (AT*)out2, H, eps));
+    return finish_launch("add2_rmsnorm_scalar");
+}
+
+int mi_geglu_tanh(const void* gu, void* out, int adtype, int64_t T, int I, cudaStream_t stream) {
+    const int64_t total = T * I;
+    if (total <= 0) return kOk;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    MI_DISPATCH_1(adtype, AT,
+        launch_dependent(geglu_tanh_kernel<AT>, dim3((int)blocks), dim3(256), 0, stream, (const AT*)gu, (AT*)out,
+                         total, I));
+    return finish_launch("geglu_tanh");
+}
+
+int mi_concat_cast(const float* hidden, const float* a, const float* b, const float* other, void* out, int adtype,
+                   int T, int H, cudaStream_t stream) {
+    if (T <= 0 || H <= 0) return kOk;
+    MI_DISPATCH_1(adtype, AT,
+        launch_dependent(concat_cast_kernel<AT>, dim3(T), dim3(256), 0, stream, hidden, a, b, other, (AT*)out, H));
+    return finish_launch("concat_cast");
+}
+
+int mi_rows_plus_vec(float* hidden, const float* y, const void* vec, int wdtype, int T, int H, cudaStream_t stream) {
+    if (T <= 0 || H <= 0) return kOk;
+    MI_DISPATCH_1(wdtype, WT,
+        launch_dependent(rows_plus_vec_kernel<WT>, dim3(T), dim3(256), 0, stream, hidden, y, (const WT*)vec, H));
+    return finish_launch("rows_plus_vec");
+}
+
+}  // extern "C"

@@ -38,10 +38,13 @@ def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0") -> Tuple[M
     :func:`configure_matmul_exactness`).  Both precision paths need them, and everything else that runs
     PyTorch products in the same process afterwards inherits them."""
     cj = read_config_json(folder)
+    source = FolderSource(folder)
+    # sizes that only a tensor's shape gives: a builder may look them up here
+    cj.setdefault("tensor_shapes", {n: tuple(source.shape(n)) for n in source.names()})
     spec = build_model_spec(cj)
     rt = _runtime(dtype, device)
     model = Model(spec)
-    model.load(FolderSource(folder), rt)
+    model.load(source, rt)
     return model, rt, cj
 
 

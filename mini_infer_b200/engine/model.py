@@ -57,6 +57,7 @@ class Model:
         # is called after every schedule entry of an eager forward pass (the reference's counterpart is
         # debug_print_tensor, src/model/transformer_model.cpp:24-61)
         self.layer_observer = None
+        self._keeps_embedding_output = any(getattr(l.block, "needs_embedding_output", False) for l in self.layers)
         self._plan_caches()
 
     # -- what the model keeps between steps --------------------------------- #
@@ -162,6 +163,8 @@ class Model:
 
     def _forward(self, ctx: StepContext, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         hidden = self.embedding.forward(ctx.token_ids)
+        if self._keeps_embedding_output:
+            ctx.embedding_output = hidden.clone()       # the residual stream is updated in place from here on
         pending = None
         schedule = self.spec.schedule
         for pos, e in enumerate(schedule):
@@ -174,6 +177,7 @@ class Model:
                 if pos + 1 < len(schedule):
                     nxt, nxt_caches = self.layers[schedule[pos + 1].layer], self.bindings[pos + 1]
                     ctx.prefetch_upcoming = lambda n=nxt, c=nxt_caches: n.block.prefetch_layer(n, ctx, c)
+            ctx.entry_args = e.args
             pending = layer.block.forward(layer, hidden, pending, ctx, self.bindings[pos])
             if self.layer_observer is not None:
                 # the addition of a part's output is left to the next norm's kernel; form it here

@@ -885,3 +885,256 @@ def sample_rows(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None
     check(library().mi_sample_rows(_ptr(logits), _ptr(temperature), _ptr(top_p), _ptr(u), _ptr(probs_scratch),
                                    _ptr(out), R, V, _stream()), "sample_rows")
     return out
+
+
+# --------------------------------------------------------------------------- #
+# residual arrangements with two parts side by side, gated feed-forward with gelu
+# --------------------------------------------------------------------------- #
+
+def add2_rmsnorm_scalar(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor],
+                        gain1: torch.Tensor, gain2: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                        rows: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """``hidden += a + b`` (each optional; written back unless ``rows``), one root mean square per row, and the
+    rows times ``gain1`` and (if given) times ``gain2``: two norms of the same residual whose weights are
+    single numbers (float32 tensors of one element on the device)."""
+    _chk(hidden, "add2_rmsnorm_scalar hidden", F32)
+    T, H = hidden.shape
+    _chk(a, "add2_rmsnorm_scalar a", F32, (T, H))
+    _chk(b, "add2_rmsnorm_scalar b", F32, (T, H))
+    _chk(rows, "add2_rmsnorm_scalar rows", I32)
+    _chk(gain1, "add2_rmsnorm_scalar gain1", F32, (1,))
+    _chk(gain2, "add2_rmsnorm_scalar gain2", F32, (1,))
+    n = T if rows is None else rows.numel()
+    out1 = torch.empty(n, H, dtype=out_dtype, device=hidden.device)
+    out2 = torch.empty(n, H, dtype=out_dtype, device=hidden.device) if gain2 is not None else None
+    if DEBUG_BOUNDS:
+        _dbg_range(rows, 0, T, "add2_rmsnorm_scalar rows")
+    check(library().mi_add2_rmsnorm_scalar(_ptr(hidden), _ptr(a), _ptr(b), _ptr(rows), _ptr(gain1), _ptr(gain2),
+                                           _ptr(out1), _ptr(out2), _code(out1, "add2_rmsnorm_scalar out"), n, H,
+                                           float(eps), _stream()), "add2_rmsnorm_scalar")
+    return out1, out2
+
+
+def geglu_tanh(gu: torch.Tensor) -> torch.Tensor:
+    """``gelu_tanh(gu[:, :I]) * gu[:, I:]`` in the type of ``gu``."""
+    _chk(gu, "geglu_tanh gu")
+    T, two_i = gu.shape
+    if two_i % 2:
+        raise ValueError("geglu_tanh: the row holds gate and up halves of equal size")
+    out = torch.empty(T, two_i // 2, dtype=gu.dtype, device=gu.device)
+    check(library().mi_geglu_tanh(_ptr(gu), _ptr(out), _code(gu, "geglu_tanh gu"), T, two_i // 2, _stream()),
+          "geglu_tanh")
+    return out
+
+
+def concat_cast(hidden: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], other: torch.Tensor,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """``[hidden + a + b | other]`` row by row in ``out_dtype`` (``hidden`` is left as it is)."""
+    _chk(hidden, "concat_cast hidden", F32)
+    T, H = hidden.shape
+    _chk(a, "concat_cast a", F32, (T, H))
+    _chk(b, "concat_cast b", F32, (T, H))
+    _chk(other, "concat_cast other", F32, (T, H))
+    out = torch.empty(T, 2 * H, dtype=out_dtype, device=hidden.device)
+    check(library().mi_concat_cast(_ptr(hidden), _ptr(a), _ptr(b), _ptr(other), _ptr(out), _code(out, "concat_cast out"),
+                                   T, H, _stream()), "concat_cast")
+    return out
+
+
+def rows_plus_vec(hidden: torch.Tensor, y: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
+    """``hidden[t] = y[t] + vec`` (float32 rows; ``vec`` float32 or bfloat16)."""
+    _chk(hidden, "rows_plus_vec hidden", F32)
+    T, H = hidden.shape
+    _chk(y, "rows_plus_vec y", F32, (T, H))
+    _chk(vec, "rows_plus_vec vec", None, (H,))
+    check(library().mi_rows_plus_vec(_ptr(hidden), _ptr(y), _ptr(vec), _code(vec, "rows_plus_vec vec"), T, H, _stream()),
+          "rows_plus_vec")
+    return hidden
+
+
+# --------------------------------------------------------------------------- #
+# mixers with a fixed-size state per request
+# --------------------------------------------------------------------------- #
+
+CONV_MAX_TAPS = 8
+
+
+def causal_conv_silu(x: torch.Tensor, col0: int, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor],
+                     state: torch.Tensor, state_offset: int, q_start: torch.Tensor, req_of_token: torch.Tensor,
+                     state_slot: torch.Tensor) -> torch.Tensor:
+    """Causal convolution over time per channel, then silu, on the columns ``col0 .. col0 + channels`` of the
+    float32 rows ``x``; returns float32 ``[T, channels]``.  ``w [channels, taps]`` (the last column weighs the
+    current token).  The ``taps - 1`` inputs before a request's portion come from ``state[slot,
+    state_offset : state_offset + (taps-1)*channels]`` (time-major), which is brought up to date afterwards."""
+    _chk(x, "causal_conv_silu x", F32)
+    T, ld = x.shape
+    C = int(channels)
+    _chk(w, "causal_conv_silu w", None, (C, None))
+    taps = w.shape[1]
+    _chk(bias, "causal_conv_silu bias", w.dtype, (C,))
+    _chk(state, "causal_conv_silu state", F32)
+    if col0 < 0 or col0 + C > ld or state.dim() != 2 or state_offset + (taps - 1) * C > state.shape[1]:
+        raise ValueError("causal_conv_silu: columns or state section out of range")
+    B = state_slot.numel()
+    _chk(q_start, "causal_conv_silu q_start", I32, (B + 1,))
+    _chk(req_of_token, "causal_conv_silu req_of_token", I32, (T,))
+    _chk(state_slot, "causal_conv_silu state_slot", I32, (B,))
+    if DEBUG_BOUNDS:
+        _dbg_range(state_slot, 0, state.shape[0], "causal_conv_silu state_slot")
+        _dbg_range(req_of_token, 0, B, "causal_conv_silu req_of_token")
+    out = torch.empty(T, C, dtype=F32, device=x.device)
+    check(library().mi_causal_conv_silu(x.data_ptr() + 4 * col0, ld, _ptr(w), _ptr(bias), _code(w, "causal_conv_silu w"),
+                                        state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start),
+                                        _ptr(req_of_token), _ptr(state_slot), _ptr(out), C, C, taps, T, B, _stream()),
+          "causal_conv_silu")
+    return out
+
+
+def delta_scan(qkv: torch.Tensor, beta_raw: torch.Tensor, beta_col: int, a_raw: torch.Tensor, a_col: int,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, state_offset: int,
+               q_start: torch.Tensor, state_slot: torch.Tensor, heads: int, key_heads: int, d: int, dv: int,
+               q_scale: float) -> torch.Tensor:
+    """Gated delta rule with a decay per head and key channel, token by token over every request's portion.
+
+    ``qkv`` float32 ``[T, 2*key_heads*d + heads*dv]`` (q | k | v after their convolutions); ``beta_raw`` holds
+    the ``heads`` write strengths before the sigmoid from column ``beta_col``; ``a_raw`` the ``heads*d`` decay
+    inputs before ``dt_bias`` and the softplus from column ``a_col``.  Per head, with unit q (times
+    ``q_scale``) and unit k: ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` where
+    ``g = exp(-exp(a_log) * softplus(a + dt_bias))``.  ``S`` (``heads x d x dv`` floats) lives in
+    ``state[slot, state_offset:]``.  Returns ``o`` float32 ``[T, heads*dv]``."""
+    _chk(qkv, "delta_scan qkv", F32)
+    T = qkv.shape[0]
+    if qkv.shape[1] != 2 * key_heads * d + heads * dv:
+        raise ValueError("delta_scan: the rows of qkv do not hold q, k and v of the given sizes")
+    _chk(beta_raw, "delta_scan beta_raw", F32)
+    _chk(a_raw, "delta_scan a_raw", F32)
+    _chk(a_log, "delta_scan a_log", F32, (heads,))
+    _chk(dt_bias, "delta_scan dt_bias", F32, (heads * d,))
+    _chk(state, "delta_scan state", F32)
+    B = state_slot.numel()
+    _chk(q_start, "delta_scan q_start", I32, (B + 1,))
+    _chk(state_slot, "delta_scan state_slot", I32, (B,))
+    if (beta_col + heads > beta_raw.shape[1] or a_col + heads * d > a_raw.shape[1]
+            or state_offset + heads * d * dv > state.shape[1]):
+        raise ValueError("delta_scan: columns or state section out of range")
+    if DEBUG_BOUNDS:
+        _dbg_range(state_slot, 0, state.shape[0], "delta_scan state_slot")
+    out = torch.empty(T, heads * dv, dtype=F32, device=qkv.device)
+    check(library().mi_delta_scan(_ptr(qkv), qkv.shape[1], beta_raw.data_ptr() + 4 * beta_col, beta_raw.shape[1],
+                                  a_raw.data_ptr() + 4 * a_col, a_raw.shape[1], _ptr(a_log), _ptr(dt_bias),
+                                  state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start), _ptr(state_slot),
+                                  _ptr(out), B, heads, key_heads, d, dv, float(q_scale), _stream()), "delta_scan")
+    return out
+
+
+def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             d_skip: torch.Tensor, state: torch.Tensor, state_offset: int, q_start: torch.Tensor,
+             state_slot: torch.Tensor, heads: int, groups: int, n_state: int, head_dim: int) -> torch.Tensor:
+    """State-space recurrence with a scalar decay per head: ``dt = softplus(dt_raw + dt_bias)``,
+    ``S <- exp(-exp(a_log) dt) S + dt B x^T``, ``y = S^T C + d_skip x``.  ``xbc`` float32
+    ``[T, heads*head_dim + 2*groups*n_state]`` (x | B | C after the convolution); ``S``
+    (``heads x n_state x head_dim`` floats) lives in ``state[slot, state_offset:]``.  Returns float32
+    ``[T, heads*head_dim]``."""
+    _chk(xbc, "ssd_scan xbc", F32)
+    T = xbc.shape[0]
+    if xbc.shape[1] != heads * head_dim + 2 * groups * n_state:
+        raise ValueError("ssd_scan: the rows of xbc do not hold x, B and C of the given sizes")
+    _chk(dt_raw, "ssd_scan dt_raw", F32)
+    for t, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        _chk(t, "ssd_scan " + name, F32, (heads,))
+    _chk(state, "ssd_scan state", F32)
+    B = state_slot.numel()
+    _chk(q_start, "ssd_scan q_start", I32, (B + 1,))
+    _chk(state_slot, "ssd_scan state_slot", I32, (B,))
+    if dt_col + heads > dt_raw.shape[1] or state_offset + heads * n_state * head_dim > state.shape[1]:
+        raise ValueError("ssd_scan: columns or state section out of range")
+    if DEBUG_BOUNDS:
+        _dbg_range(state_slot, 0, state.shape[0], "ssd_scan state_slot")
+    out = torch.empty(T, heads * head_dim, dtype=F32, device=xbc.device)
+    check(library().mi_ssd_scan(_ptr(xbc), xbc.shape[1], dt_raw.data_ptr() + 4 * dt_col, dt_raw.shape[1], _ptr(dt_bias),
+                                _ptr(a_log), _ptr(d_skip), state.data_ptr() + 4 * state_offset, state.shape[1],
+                                _ptr(q_start), _ptr(state_slot), _ptr(out), B, heads, groups, n_state, head_dim,
+                                _stream()), "ssd_scan")
+    return out
+
+
+def gated_group_rmsnorm(y: torch.Tensor, gate: torch.Tensor, gate_col: int, weight: torch.Tensor, groups: int,
+                        gate_first: bool, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """RMS norm over ``groups`` equal parts of every float32 row of ``y`` with a gate from the columns
+    ``gate_col ..`` of ``gate``: ``gate_first``: ``norm(y * silu(gate)) * w``; else ``norm(y) * w *
+    sigmoid(gate)``.  Column ``c`` uses ``weight[c % len(weight)]``."""
+    _chk(y, "gated_group_rmsnorm y", F32)
+    T, n = y.shape
+    _chk(gate, "gated_group_rmsnorm gate", F32)
+    _chk(weight, "gated_group_rmsnorm weight")
+    if gate.shape[0] != T or gate_col + n > gate.shape[1] or n % groups or n % weight.numel():
+        raise ValueError("gated_group_rmsnorm: gate columns, groups or weight do not fit the rows")
+    out = torch.empty(T, n, dtype=out_dtype, device=y.device)
+    check(library().mi_gated_group_rmsnorm(_ptr(y), gate.data_ptr() + 4 * gate_col, gate.shape[1], _ptr(weight),
+                                           _code(weight, "gated_group_rmsnorm weight"), weight.numel(), _ptr(out),
+                                           _code(out, "gated_group_rmsnorm out"), T, n, int(groups),
+                                           0 if gate_first else 1, float(eps), _stream()), "gated_group_rmsnorm")
+    return out
+
+
+# --------------------------------------------------------------------------- #
+# attention with capped scores mixed over the heads
+# --------------------------------------------------------------------------- #
+
+def rope_store(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dim: int,
+               slot_mapping: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, nh: int, nkv: int,
+               dk: int, dv: int, page_size: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """Rotary encoding of the first ``rot_dim`` dimensions of the query and key heads of float32 rows
+    ``[nh*dk | nkv*dk | nkv*dv]``, cache write of keys ``[pages, nkv, page_size, dk]`` and values
+    ``[pages, nkv, page_size, dv]`` (slot -1: not written).  Returns ``q [T, nh, dk]`` in ``out_dtype``."""
+    _chk(qkv, "rope_store qkv", F32)
+    T = qkv.shape[0]
+    _chk(qkv, "rope_store qkv", F32, (T, (nh + nkv) * dk + nkv * dv))
+    _chk(positions, "rope_store positions", I32, (T,))
+    _chk(inv_freq, "rope_store inv_freq", F32)
+    if rot_dim and (inv_freq is None or inv_freq.numel() != rot_dim // 2):
+        raise ValueError(f"rope_store: {rot_dim} rotary dims need {rot_dim // 2} frequencies")
+    _chk(slot_mapping, "rope_store slot_mapping", I32, (T,))
+    _chk(k_cache, "rope_store k_cache", out_dtype, (None, nkv, page_size, dk))
+    _chk(v_cache, "rope_store v_cache", out_dtype, (None, nkv, page_size, dv))
+    q = torch.empty(T, nh, dk, dtype=out_dtype, device=qkv.device)
+    if DEBUG_BOUNDS:
+        _dbg_range(slot_mapping, -1, k_cache.shape[0] * page_size, "rope_store slot_mapping")
+    check(library().mi_rope_store(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slot_mapping), _ptr(q),
+                                  _ptr(k_cache), _ptr(v_cache), _code(q, "rope_store q"), T, nh, nkv, dk, dv,
+                                  int(rot_dim), page_size, _stream()), "rope_store")
+    return q
+
+
+def attention_mix_supported(nh: int, nkv: int, dk: int, dv: int, dtype: torch.dtype) -> bool:
+    return bool(library().mi_attn_mix_supported(nh, nkv, dk, dv, 4 if dtype == F32 else 2))
+
+
+def attention_mix(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, mix: Optional[torch.Tensor],
+                  block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int,
+                  window: int, scale: float, softcap: float) -> torch.Tensor:
+    """Attention of a ragged batch over the paged cache with ``score <- softcap * tanh(score / softcap)``
+    (``softcap`` 0: none) and then ``score_h <- sum_g mix[h, g] score_g`` (``mix`` None: none) before the
+    softmax over the visible keys.  Returns ``[T, nh, dv]``."""
+    _chk(q, "attention_mix q")
+    T, nh, dk = q.shape
+    _chk(k_cache, "attention_mix k_cache", q.dtype)
+    _, nkv, page_size, dk2 = k_cache.shape
+    _chk(v_cache, "attention_mix v_cache", q.dtype, (k_cache.shape[0], nkv, page_size, None))
+    dv = v_cache.shape[3]
+    if dk2 != dk:
+        raise ValueError(f"attention_mix: key size of q ({dk}) and of the cache ({dk2}) differ")
+    _chk(mix, "attention_mix mix", F32, (nh, nh))
+    _chk(block_table, "attention_mix block_table", I32)
+    B, max_pages = block_table.shape
+    _chk(q_start, "attention_mix q_start", I32, (B + 1,))
+    _chk(kv_len, "attention_mix kv_len", I32, (B,))
+    out = torch.empty(T, nh, dv, dtype=q.dtype, device=q.device)
+    if DEBUG_BOUNDS:
+        _dbg_batch("attention_mix", q_start, kv_len, block_table, T, k_cache.shape[0], page_size, int(window),
+                   int(max_q_len))
+    check(library().mi_attn_mix(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "attention_mix q"), _ptr(mix),
+                                _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), B, int(max_q_len), nh, nkv,
+                                dk, dv, page_size, max_pages, int(window), float(scale), float(softcap), _stream()),
+          "attention_mix")
+    return out

@@ -47,6 +47,16 @@ _SIGNATURES = {
     "mi_random_fill": [P, I, L, ctypes.c_uint, ctypes.c_uint, F, F, P],
     "mi_dense_f32": [P, P, P, I, I, I, P],
     "mi_l2_prefetch": [P, ctypes.c_ulonglong, P],
+    "mi_causal_conv_silu": [P, I, P, P, I, P, L, P, P, P, P, I, I, I, I, I, P],
+    "mi_delta_scan": [P, I, P, I, P, I, P, P, P, L, P, P, P, I, I, I, I, I, F, P],
+    "mi_ssd_scan": [P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, P],
+    "mi_gated_group_rmsnorm": [P, P, I, P, I, I, P, I, I, I, I, I, F, P],
+    "mi_rope_store": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
+    "mi_attn_mix": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P],
+    "mi_add2_rmsnorm_scalar": [P, P, P, P, P, P, P, P, I, I, I, F, P],
+    "mi_geglu_tanh": [P, P, I, L, I, P],
+    "mi_concat_cast": [P, P, P, P, P, I, I, I, P],
+    "mi_rows_plus_vec": [P, P, P, I, I, I, P],
 }
 
 
@@ -95,6 +105,8 @@ def library() -> ctypes.CDLL:
     lib.mi_qkv_skinny_supported.restype = c_int
     lib.mi_dense_skinny_max_rows.argtypes = []
     lib.mi_dense_skinny_max_rows.restype = c_int
+    lib.mi_attn_mix_supported.argtypes = [I, I, I, I, I]
+    lib.mi_attn_mix_supported.restype = c_int
     lib.mi_attn_decode_split_size.argtypes = []
     lib.mi_attn_decode_split_size.restype = c_int
     _lib = lib

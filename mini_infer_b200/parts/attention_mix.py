@@ -1,0 +1,92 @@
+"""Attention over the paged cache whose heads exchange their scores before the softmax.
+
+``score = (q . k) * scale``; ``score <- softcap * tanh(score / softcap)`` (if a cap is set); then every
+head's score of a (query, key) pair becomes a mix of all heads' scores of that pair,
+``score_h <- sum_g talk[h, g] * score_g`` (if the layer has such a matrix); then the softmax over the keys a
+window lets through.  Query/key heads and value heads may differ in size.  One library product for q, k and
+v together, one kernel for rotation and cache write, one attention kernel that owns all heads of its
+queries (the mix couples them), one library product for the output.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.registry import part_class, register_part
+from ..config.spec import PartSpec
+from ..ops import functional as F
+from .base import CacheBinding, KVNeed, Mixer, Runtime, StepContext, TensorDecl, linear
+
+
+class HeadMixAttention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim`` (queries and keys),
+    ``value_dim``, ``window`` (0 = all keys), ``scale``, ``softcap`` (0 = none), ``head_mix`` (the layer has a
+    ``[heads, heads]`` matrix that mixes the heads' scores), ``position`` (a ``PartSpec`` of category
+    ``position``), optional tensor names ``q``, ``k``, ``v``, ``o``, ``mix`` below the prefix.
+
+    Tensors: ``<prefix>q [heads*head_dim, hidden]``, ``<prefix>k [kv_heads*head_dim, hidden]``,
+    ``<prefix>v [kv_heads*value_dim, hidden]``, ``<prefix>o [hidden, heads*value_dim]``,
+    ``<prefix>talk [heads, heads]`` if ``head_mix``."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        p = self.params
+        self.H = int(p["hidden_size"])
+        self.nh = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.dk = int(p["head_dim"])
+        self.dv = int(p.get("value_dim", self.dk))
+        self.window = int(p.get("window", 0))
+        self.scale = float(p.get("scale", self.dk ** -0.5))
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        self.head_mix = bool(p.get("head_mix", False))
+        pos: PartSpec = p.get("position") or PartSpec("none")
+        self.position = part_class("position", pos.kind)(pos.params, prefix)
+        if self.nkv < 1 or self.nh % self.nkv:
+            raise ValueError(f"attention: {self.nh} heads are not a multiple of {self.nkv} key/value heads")
+        self.names = {k: prefix + p.get(k, d) for k, d in (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"), ("mix", "talk"))}
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        n = self.names
+        out = [TensorDecl(n["q"], (self.nh * self.dk, self.H)), TensorDecl(n["k"], (self.nkv * self.dk, self.H)),
+               TensorDecl(n["v"], (self.nkv * self.dv, self.H))]
+        if self.head_mix:
+            out.append(TensorDecl(n["mix"], (self.nh, self.nh), "head_mix"))
+        out.append(TensorDecl(n["o"], (self.H, self.nh * self.dv)))
+        return out
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        m, dev, n = rt.precision.matrix, rt.device, self.names
+        self.w_qkv = torch.cat([m(tensors[n[k]], dev) for k in ("q", "k", "v")], dim=0)
+        self.w_o = m(tensors[n["o"]], dev)
+        # the mix acts on float scores
+        self.mix = tensors[n["mix"]].to(device=dev, dtype=torch.float32).contiguous() if self.head_mix else None
+        self.inv_freq = self.position.table(dev)
+        self.rot_dim = self.position.rot_dim if self.inv_freq is not None else 0
+        if not F.attention_mix_supported(self.nh, self.nkv, self.dk, self.dv, rt.act):
+            raise ValueError(f"attention: {self.nh} heads of key size {self.dk} and value size {self.dv} "
+                             f"are more than one block of the kernel holds")
+
+    def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
+        F.l2_prefetch(self.w_qkv)
+
+    def cache_need(self):
+        return KVNeed(self.nkv, self.dk, self.window, value_dim=self.dv)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        view = ctx.kv_groups[cache.group]
+        kc, vc = view.k[cache.layer_slot], view.v[cache.layer_slot]
+        qkv = linear(x, self.w_qkv, torch.float32)
+        q = F.rope_store(qkv, ctx.positions, self.inv_freq, self.rot_dim, view.slot_mapping, kc, vc, self.nh,
+                         self.nkv, self.dk, self.dv, view.page_size, self.rt.act)
+        a = F.attention_mix(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
+                            self.window, self.scale, self.softcap)
+        return linear(a.view(ctx.num_tokens, self.nh * self.dv), self.w_o, torch.float32)
+
+
+register_part("mixer", "head_mix_attention", HeadMixAttention)

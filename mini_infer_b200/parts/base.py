@@ -190,6 +190,10 @@ class StepContext:
     # the last rows of the step (one token each) belong to no request: they fill a captured batch up to its
     # size, are written nowhere and their logits are dropped
     rows_of_no_request: int = 0
+    # the arguments of the schedule entry that is running (``ScheduleEntry.args``), set by the model
+    entry_args: Mapping[str, Any] = field(default_factory=dict)
+    # the embedding's output [T, H] float32, kept aside for blocks that declare ``needs_embedding_output``
+    embedding_output: Optional[torch.Tensor] = None
     # host copies, for parts written in plain PyTorch (tests' toy parts)
     host_q_start: Sequence[int] = ()
     host_kv_len: Sequence[int] = ()
@@ -260,6 +264,28 @@ class WeightedRowSum(Deferred):
     def materialize(self) -> torch.Tensor:
         from ..ops import functional as F
         return F.moe_combine(self.rows, self.index, self.weights, self.extra, self.scale)
+
+
+@dataclass
+class TensorSum(Deferred):
+    """``a + b`` of two float32 tensors of one shape, not added yet (the outputs of two parts that read
+    the same residual)."""
+
+    a: torch.Tensor
+    b: torch.Tensor
+
+    def materialize(self) -> torch.Tensor:
+        return self.a + self.b
+
+
+def split_sum(pending):
+    """``(a, b)`` with ``pending = a + b`` (either may be None) for a consumer whose kernel adds up to two
+    pending tensors itself."""
+    if pending is None:
+        return None, None
+    if isinstance(pending, TensorSum):
+        return pending.a, pending.b
+    return resolve(pending), None
 
 
 def resolve(pending):

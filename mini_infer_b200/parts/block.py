@@ -17,8 +17,8 @@ import torch
 
 from ..config.registry import register_part
 from ..ops import functional as F
-from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, StepContext, TensorDecl,
-                   apply_norm, linear)
+from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, StepContext, TensorDecl, TensorSum,
+                   apply_norm, linear, split_sum)
 
 
 class PreNormResidual(Block):
@@ -36,17 +36,21 @@ class PreNormResidual(Block):
 
 
 class TokenEmbedding(Embedding):
-    """params: ``vocab_size``, ``hidden_size``.  Tensor: ``<prefix>weight [V, H]``; no scaling
+    """params: ``vocab_size``, ``hidden_size``, optional ``tensor`` (the tensor's name below the prefix,
+    default ``weight``).  Tensor: ``<prefix>weight [V, H]``; no scaling
     (src/model/transformer_model.cpp:561-565)."""
 
     graph_safe = True
 
+    def _name(self) -> str:
+        return self.prefix + self.params.get("tensor", "weight")
+
     def tensor_decls(self) -> List[TensorDecl]:
-        return [TensorDecl(self.prefix + "weight", (self.params["vocab_size"], self.params["hidden_size"]))]
+        return [TensorDecl(self._name(), (self.params["vocab_size"], self.params["hidden_size"]))]
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
-        self.weight = rt.precision.matrix(tensors[self.prefix + "weight"], rt.device)
+        self.weight = rt.precision.matrix(tensors[self._name()], rt.device)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         return F.embed_gather(token_ids, self.weight)
@@ -54,21 +58,25 @@ class TokenEmbedding(Embedding):
 
 class LinearHead(LMHead):
     """params: ``vocab_size``, ``hidden_size``, ``tied_to`` (name of the embedding tensor, or
-    None).  Tensor: ``<prefix>weight [V, H]`` unless tied (src/model/transformer_model.cpp:355-361;
+    None), optional ``tensor`` (the tensor's name below the prefix, default ``weight``).  Tensor:
+    ``<prefix>weight [V, H]`` unless tied (src/model/transformer_model.cpp:355-361;
     the reference deep-copies the tied matrix, here it is the same storage)."""
 
     graph_safe = True
 
+    def _name(self) -> str:
+        return self.prefix + self.params.get("tensor", "weight")
+
     def tensor_decls(self) -> List[TensorDecl]:
         if self.params.get("tied_to"):
             return []
-        return [TensorDecl(self.prefix + "weight", (self.params["vocab_size"], self.params["hidden_size"]))]
+        return [TensorDecl(self._name(), (self.params["vocab_size"], self.params["hidden_size"]))]
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         self.weight = None
         if not self.params.get("tied_to"):
-            self.weight = rt.precision.matrix(tensors[self.prefix + "weight"], rt.device)
+            self.weight = rt.precision.matrix(tensors[self._name()], rt.device)
 
     def tie(self, embedding_weight: torch.Tensor) -> None:
         self.weight = embedding_weight
@@ -77,6 +85,79 @@ class LinearHead(LMHead):
         return linear(x, self.weight, torch.float32)
 
 
+class ParallelResidual(Block):
+    """``x <- x + Mixer(Norm1(x)) + FFN(Norm2(x))``: both parts read the same residual and their outputs
+    are added together.  params: ``feed_forward`` (default True; False: a layer of a mixer alone, with the
+    roles ``mixer_norm`` and ``mixer`` only).
+
+    The two outputs travel on as one pending sum (:class:`TensorSum`) and are added by whatever reads the
+    residual next.  When both norms are :class:`~mini_infer_b200.parts.norm.ScalarRMSNorm` with the same
+    epsilon they differ by a factor only, and one kernel adds what is pending, takes the root mean square
+    once and writes both inputs."""
+
+    graph_safe = True
+    accepts_deferred = True
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.has_ff = bool(self.params.get("feed_forward", True))
+        self.roles = {"mixer_norm": "norm", "mixer": "mixer"}
+        if self.has_ff:
+            self.roles.update({"feed_forward_norm": "norm", "feed_forward": "feed_forward"})
+
+    def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, caches):
+        n1 = layer.mixer_norm
+        if not self.has_ff:
+            x1 = apply_norm(n1, hidden, pending)
+            return layer.mixer.forward(x1, ctx, caches.get("mixer"))
+        n2 = layer.feed_forward_norm
+        pair = getattr(n1, "apply_pair", None)
+        if pair is not None and getattr(n2, "scalar_gain", None) is not None and n2.eps == n1.eps:
+            x1, x2 = pair(hidden, pending, n2)
+        else:
+            x1 = apply_norm(n1, hidden, pending)
+            x2 = apply_norm(n2, hidden, None)
+        y = layer.mixer.forward(x1, ctx, caches.get("mixer"))
+        f = layer.feed_forward.forward(x2, ctx)
+        return TensorSum(y, f)
+
+    def prefetch_layer(self, layer: BuiltLayer, ctx: StepContext, caches) -> None:
+        layer.mixer.prefetch_first(ctx, caches.get("mixer"))
+
+
+class StreamMerge(Block):
+    """A run of no parts that re-enters the embedding into the residual stream:
+    ``x <- W [x ; x0] + step[pass]`` with ``x0`` the embedding's output, ``W [H, 2H]`` (the columns of ``x``
+    first) and one row of ``step [passes, H]`` chosen by the schedule entry's ``pass`` argument.  It stands
+    before the first layer of every pass of a stretch of layers that runs several times.
+
+    params: ``hidden_size``, ``passes``, ``weight`` and ``step`` (tensor names below the prefix)."""
+
+    graph_safe = True
+    accepts_deferred = True
+    needs_embedding_output = True
+    roles: dict = {}
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        H, n = int(self.params["hidden_size"]), int(self.params["passes"])
+        return [TensorDecl(self.prefix + self.params.get("weight", "in"), (H, 2 * H)),
+                TensorDecl(self.prefix + self.params.get("step", "step"), (n, H), "bias")]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        self.w = rt.precision.matrix(tensors[self.prefix + self.params.get("weight", "in")], rt.device)
+        self.step = rt.precision.small(tensors[self.prefix + self.params.get("step", "step")], rt.device)
+
+    def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, caches):
+        a, b = split_sum(pending)
+        t = int(ctx.entry_args.get("pass", 0))
+        both = F.concat_cast(hidden, a, b, ctx.embedding_output, self.rt.act)
+        F.rows_plus_vec(hidden, linear(both, self.w, torch.float32), self.step[t])
+        return None
+
+
 register_part("block", "prenorm_residual", PreNormResidual)
+register_part("block", "parallel_residual", ParallelResidual)
+register_part("block", "stream_merge", StreamMerge)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("lm_head", "linear", LinearHead)

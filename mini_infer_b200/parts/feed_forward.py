@@ -49,6 +49,45 @@ class SwiGLUMLP(FeedForward):
         return linear(linear_swiglu(x, self.w_gate_up, self.rt.act), self.w_down, torch.float32)
 
 
+class GatedMLP(FeedForward):
+    """``(act(x Wg^T) * (x Wu^T)) Wd^T`` with a choice of ``act``.  params: ``hidden_size``,
+    ``intermediate_size``, ``activation`` (``silu`` | ``gelu_tanh``), optional ``gate``, ``up``, ``down``
+    (tensor names below the prefix; default ``gate_proj.weight`` and so on).
+
+    Tensors: ``<prefix><gate>, <prefix><up> [I, H]``, ``<prefix><down> [H, I]``."""
+
+    graph_safe = True
+    ACTIVATIONS = ("silu", "gelu_tanh")
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.H = int(self.params["hidden_size"])
+        self.I = int(self.params["intermediate_size"])
+        self.activation = self.params.get("activation", "silu")
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation '{self.activation}' is not one of {self.ACTIVATIONS}")
+        self.names = [self.prefix + self.params.get(k, k + "_proj.weight") for k in ("gate", "up", "down")]
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        g, u, d = self.names
+        return [TensorDecl(g, (self.I, self.H)), TensorDecl(u, (self.I, self.H)), TensorDecl(d, (self.H, self.I))]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        m, dev = rt.precision.matrix, rt.device
+        g, u, d = self.names
+        self.w_gate_up = torch.cat([m(tensors[g], dev), m(tensors[u], dev)], dim=0)
+        self.w_down = m(tensors[d], dev)
+
+    def prefetch_first(self, ctx, cache=None) -> None:
+        F.l2_prefetch(self.w_gate_up)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        if self.activation == "silu":
+            return linear(linear_swiglu(x, self.w_gate_up, self.rt.act), self.w_down, torch.float32)
+        return linear(F.geglu_tanh(linear(x, self.w_gate_up, self.rt.act)), self.w_down, torch.float32)
+
+
 class SparseMoE(FeedForward):
     """Softmax router, top-k routed SwiGLU experts, optional sigmoid-gated shared expert.
 
@@ -267,5 +306,6 @@ class SparseMoE(FeedForward):
         return WeightedRowSum(y, inv_perm, w, shared, gate if shared is not None else None)
 
 
+register_part("feed_forward", "gated_mlp", GatedMLP)
 register_part("feed_forward", "swiglu_mlp", SwiGLUMLP)
 register_part("feed_forward", "sparse_moe", SparseMoE)

@@ -12,7 +12,7 @@ import torch
 
 from ..config.registry import register_part
 from ..ops import functional as F
-from .base import Deferred, Norm, Runtime, TensorDecl, WeightedRowSum
+from .base import Deferred, Norm, Runtime, TensorDecl, WeightedRowSum, split_sum
 
 
 class RMSNorm(Norm):
@@ -43,4 +43,33 @@ class RMSNorm(Norm):
         return F.add_rmsnorm(hidden, delta, self.weight, self.eps, self.rt.act, rows)
 
 
+class ScalarRMSNorm(Norm):
+    """``x / sqrt(mean(x^2) + eps) * g`` with ONE number ``g`` for all coordinates.  params: ``eps``, optional
+    ``tensor`` (the tensor's name below the prefix, default ``weight``).  Tensor: ``<prefix><tensor> []``."""
+
+    graph_safe = True
+    accepts_deferred = True
+
+    def _name(self) -> str:
+        return self.prefix + self.params.get("tensor", "weight")
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        return [TensorDecl(self._name(), (), "norm")]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        self.eps = float(self.params["eps"])
+        self.scalar_gain = tensors[self._name()].to(device=rt.device, dtype=torch.float32).reshape(1).contiguous()
+
+    def apply(self, hidden: torch.Tensor, delta, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        a, b = split_sum(delta)
+        return F.add2_rmsnorm_scalar(hidden, a, b, self.scalar_gain, None, self.eps, self.rt.act, rows)[0]
+
+    def apply_pair(self, hidden: torch.Tensor, delta, other: "ScalarRMSNorm"):
+        """This norm and ``other`` (same epsilon) of the same rows in one kernel."""
+        a, b = split_sum(delta)
+        return F.add2_rmsnorm_scalar(hidden, a, b, self.scalar_gain, other.scalar_gain, self.eps, self.rt.act)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "rmsnorm_scalar", ScalarRMSNorm)

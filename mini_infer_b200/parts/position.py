@@ -14,6 +14,7 @@ that returns another table and ``rot_dim``; the kernel takes both as arguments.
 
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -45,6 +46,29 @@ class RotaryEncoding(PositionEncoding):
         return self._table[key]
 
 
+class ScaledRotaryEncoding(RotaryEncoding):
+    """Rotary frequencies rescaled by wavelength (the rule Llama 3.1 introduced for long contexts).
+
+    params: as ``rope``, plus ``factor``, ``low``, ``high``, ``original``.  With wavelength
+    ``l = 2 pi / f``: ``f`` stays where ``l < original / high``; becomes ``f / factor`` where
+    ``l > original / low``; and in between, with ``s = (original / l - low) / (high - low)``, becomes
+    ``(1 - s) f / factor + s f``."""
+
+    def table(self, device) -> Optional[torch.Tensor]:
+        key = str(device)
+        if key not in self._table:
+            p = self.params
+            factor, low, high, original = (float(p[k]) for k in ("factor", "low", "high", "original"))
+            i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
+            f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.rot_dim)
+            wavelength = 2.0 * math.pi / f
+            s = (original / wavelength - low) / (high - low)
+            blended = (1.0 - s) * f / factor + s * f
+            f = torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, blended))
+            self._table[key] = f.to(torch.float32).to(device)
+        return self._table[key]
+
+
 class NoPositionEncoding(PositionEncoding):
     graph_safe = True
     rot_dim = 0
@@ -54,4 +78,5 @@ class NoPositionEncoding(PositionEncoding):
 
 
 register_part("position", "rope", RotaryEncoding)
+register_part("position", "rope_scaled", ScaledRotaryEncoding)
 register_part("position", "none", NoPositionEncoding)

@@ -1,0 +1,188 @@
+"""Mixers that keep a fixed-size state per request instead of a cache that grows with the context.
+
+``channel_gated_delta``: the delta rule with a write strength per head and a decay per head and key channel.
+With ``q``, ``k`` unit vectors per head (``q`` also times ``dim^-1/2``), ``beta = sigmoid(W_b h)`` and
+``g = exp(-exp(A_log) * softplus(W_a2 W_a1 h + dt_bias))`` laid out heads x dim::
+
+    S <- diag(g) S ;   u = beta (v - S^T k) ;   S <- S + k u^T ;   o = S^T q
+
+and the output is ``rmsnorm_per_head(o) * norm * sigmoid(W_g2 W_g1 h)`` through ``W_o``.  ``q``, ``k`` and ``v``
+pass a short causal convolution and silu first.
+
+``mamba2``: the state-space recurrence ``S <- exp(-exp(A_log) dt) S + dt B x^T``, ``y = S^T C + D x`` with
+``dt = softplus(dt + dt_bias)``, ``x``, ``B``, ``C`` behind one causal convolution with bias and silu,
+``y * silu(z)`` normalised in groups, through ``W_o``.
+
+Both keep ``S`` and the last ``taps - 1`` inputs of their convolutions in one float32 row per request
+(:class:`StateNeed`), are computed in float32 beyond the projections, and walk a request's tokens in order
+whatever the cut of the step.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.registry import register_part
+from ..ops import functional as F
+from .base import CacheBinding, Mixer, Runtime, StateNeed, StepContext, TensorDecl, linear
+
+
+def _f32(t: torch.Tensor, dev) -> torch.Tensor:
+    return t.to(device=dev, dtype=torch.float32).contiguous()
+
+
+class ChannelGatedDelta(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads`` (heads of q and k), ``head_dim`` (q, k),
+    ``value_dim``, ``conv`` (taps), ``decay_rank``, ``gate_rank``, ``eps`` (of the output norm).
+
+    Tensors below the prefix: ``q``, ``k`` ``[kv_heads*head_dim, hidden]``, ``v [heads*value_dim, hidden]``,
+    each with ``.conv [channels, taps]``; ``b [heads, hidden]``; ``a1 [decay_rank, hidden]``,
+    ``a2 [heads*head_dim, decay_rank]``, ``dt_bias [heads*head_dim]``, ``A_log [heads]``;
+    ``g1 [gate_rank, hidden]``, ``g2 [heads*value_dim, gate_rank]``; ``norm [value_dim]``;
+    ``o [hidden, heads*value_dim]``."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        p = self.params
+        self.H = int(p["hidden_size"])
+        self.nh = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.d = int(p["head_dim"])
+        self.dv = int(p["value_dim"])
+        self.taps = int(p["conv"])
+        self.ra = int(p["decay_rank"])
+        self.rg = int(p["gate_rank"])
+        self.eps = float(p["eps"])
+        if self.nkv < 1 or self.nh % self.nkv:
+            raise ValueError(f"delta rule: {self.nh} heads are not a multiple of {self.nkv} key heads")
+        if not 1 <= self.taps <= F.CONV_MAX_TAPS:
+            raise ValueError(f"delta rule: a convolution of {self.taps} taps (at most {F.CONV_MAX_TAPS})")
+        self.n_qk = self.nkv * self.d
+        self.n_v = self.nh * self.dv
+        self.channels = 2 * self.n_qk + self.n_v
+        self.state_floats = self.nh * self.d * self.dv
+        self.conv_floats = (self.taps - 1) * self.channels
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        p = self.prefix
+        return [TensorDecl(p + "q", (self.n_qk, self.H)), TensorDecl(p + "q.conv", (self.n_qk, self.taps), "conv"),
+                TensorDecl(p + "k", (self.n_qk, self.H)), TensorDecl(p + "k.conv", (self.n_qk, self.taps), "conv"),
+                TensorDecl(p + "v", (self.n_v, self.H)), TensorDecl(p + "v.conv", (self.n_v, self.taps), "conv"),
+                TensorDecl(p + "b", (self.nh, self.H)), TensorDecl(p + "A_log", (self.nh,), "bias"),
+                TensorDecl(p + "norm", (self.dv,), "norm"),
+                TensorDecl(p + "a1", (self.ra, self.H)), TensorDecl(p + "a2", (self.nh * self.d, self.ra), "low_rank"),
+                TensorDecl(p + "dt_bias", (self.nh * self.d,), "bias"),
+                TensorDecl(p + "g1", (self.rg, self.H)), TensorDecl(p + "g2", (self.n_v, self.rg), "low_rank"),
+                TensorDecl(p + "o", (self.H, self.n_v))]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        m, dev, p = rt.precision.matrix, rt.device, self.prefix
+        self.w_in = torch.cat([m(tensors[p + n], dev) for n in ("q", "k", "v", "b")], dim=0)
+        self.w_low = torch.cat([m(tensors[p + "a1"], dev), m(tensors[p + "g1"], dev)], dim=0)
+        # both second projections as one product: [a2 0; 0 g2] on [a1 h ; g1 h]
+        w_up = torch.zeros(self.nh * self.d + self.n_v, self.ra + self.rg, dtype=rt.act, device=dev)
+        w_up[:self.nh * self.d, :self.ra] = m(tensors[p + "a2"], dev)
+        w_up[self.nh * self.d:, self.ra:] = m(tensors[p + "g2"], dev)
+        self.w_up = w_up
+        self.w_conv = torch.cat([_f32(tensors[p + n + ".conv"], dev) for n in ("q", "k", "v")], dim=0)
+        self.a_log = _f32(tensors[p + "A_log"], dev)
+        self.dt_bias = _f32(tensors[p + "dt_bias"], dev)
+        self.norm_w = _f32(tensors[p + "norm"], dev)
+        self.w_o = m(tensors[p + "o"], dev)
+
+    def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
+        F.l2_prefetch(self.w_in)
+
+    def cache_need(self):
+        return StateNeed((self.state_floats + self.conv_floats,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        state = ctx.states[cache.group]
+        proj = linear(x, self.w_in, torch.float32)                       # q | k | v | beta
+        low = linear(x, self.w_low, self.rt.act)
+        up = linear(low, self.w_up, torch.float32)                       # decay input | gate input
+        qkv = F.causal_conv_silu(proj, 0, self.channels, self.w_conv, None, state, self.state_floats,
+                                 ctx.q_start, ctx.req_of_token, ctx.state_slot)
+        o = F.delta_scan(qkv, proj, self.channels, up, 0, self.a_log, self.dt_bias, state, 0, ctx.q_start,
+                         ctx.state_slot, self.nh, self.nkv, self.d, self.dv, self.d ** -0.5)
+        y = F.gated_group_rmsnorm(o, up, self.nh * self.d, self.norm_w, self.nh, False, self.eps, self.rt.act)
+        return linear(y, self.w_o, torch.float32)
+
+
+class Mamba2(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``head_dim``, ``state_size``, ``groups`` (of B and C),
+    ``norm_groups``, ``conv`` (taps), ``eps``.
+
+    Tensors below the prefix: ``in [2*inner + 2*groups*state + heads, hidden]`` (rows z | x | B | C | dt),
+    ``conv [inner + 2*groups*state, taps]``, ``conv.b``, ``dt_bias``, ``A_log``, ``D`` ``[heads]``,
+    ``norm [inner]``, ``o [hidden, inner]``; ``inner = heads * head_dim``."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        p = self.params
+        self.H = int(p["hidden_size"])
+        self.nh = int(p["num_heads"])
+        self.P = int(p["head_dim"])
+        self.N = int(p["state_size"])
+        self.G = int(p.get("groups", 1))
+        self.norm_groups = int(p.get("norm_groups", 1))
+        self.taps = int(p["conv"])
+        self.eps = float(p["eps"])
+        self.inner = self.nh * self.P
+        if self.G < 1 or self.nh % self.G:
+            raise ValueError(f"mamba2: {self.nh} heads are not a multiple of {self.G} groups")
+        if self.norm_groups < 1 or self.inner % self.norm_groups:
+            raise ValueError(f"mamba2: {self.inner} channels do not split into {self.norm_groups} norm groups")
+        if not 1 <= self.taps <= F.CONV_MAX_TAPS:
+            raise ValueError(f"mamba2: a convolution of {self.taps} taps (at most {F.CONV_MAX_TAPS})")
+        self.channels = self.inner + 2 * self.G * self.N
+        self.state_floats = self.nh * self.N * self.P
+        self.conv_floats = (self.taps - 1) * self.channels
+
+    def tensor_decls(self) -> List[TensorDecl]:
+        p = self.prefix
+        return [TensorDecl(p + "in", (2 * self.inner + 2 * self.G * self.N + self.nh, self.H)),
+                TensorDecl(p + "conv", (self.channels, self.taps), "conv"),
+                TensorDecl(p + "conv.b", (self.channels,), "bias"),
+                TensorDecl(p + "dt_bias", (self.nh,), "bias"), TensorDecl(p + "A_log", (self.nh,), "bias"),
+                TensorDecl(p + "D", (self.nh,), "norm"), TensorDecl(p + "norm", (self.inner,), "norm"),
+                TensorDecl(p + "o", (self.H, self.inner))]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        m, dev, p = rt.precision.matrix, rt.device, self.prefix
+        self.w_in = m(tensors[p + "in"], dev)
+        self.w_conv = _f32(tensors[p + "conv"], dev)
+        self.b_conv = _f32(tensors[p + "conv.b"], dev)
+        self.dt_bias = _f32(tensors[p + "dt_bias"], dev)
+        self.a_log = _f32(tensors[p + "A_log"], dev)
+        self.d_skip = _f32(tensors[p + "D"], dev)
+        self.norm_w = _f32(tensors[p + "norm"], dev)
+        self.w_o = m(tensors[p + "o"], dev)
+
+    def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
+        F.l2_prefetch(self.w_in)
+
+    def cache_need(self):
+        return StateNeed((self.state_floats + self.conv_floats,), torch.float32)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
+        state = ctx.states[cache.group]
+        proj = linear(x, self.w_in, torch.float32)                       # z | x | B | C | dt
+        xbc = F.causal_conv_silu(proj, self.inner, self.channels, self.w_conv, self.b_conv, state,
+                                 self.state_floats, ctx.q_start, ctx.req_of_token, ctx.state_slot)
+        y = F.ssd_scan(xbc, proj, self.inner + self.channels, self.dt_bias, self.a_log, self.d_skip, state, 0,
+                       ctx.q_start, ctx.state_slot, self.nh, self.G, self.N, self.P)
+        y = F.gated_group_rmsnorm(y, proj, 0, self.norm_w, self.norm_groups, True, self.eps, self.rt.act)
+        return linear(y, self.w_o, torch.float32)
+
+
+register_part("mixer", "channel_gated_delta", ChannelGatedDelta)
+register_part("mixer", "mamba2", Mamba2)

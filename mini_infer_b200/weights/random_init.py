@@ -78,6 +78,11 @@ def random_tensor(shape: Tuple[int, ...], key: Tuple[int, int], std: float, offs
     return torch.from_numpy(random_values_host(n, key, std, offset)).reshape(tuple(shape)).to(dtype)
 
 
+# role of a tensor -> (mean, factor on the standard deviation): short filters and small matrices that act
+# on few inputs are drawn wider, so that what they feed is not vanishingly small
+ROLE_INIT = {"norm": (1.0, 1.0), "conv": (0.0, 15.0), "low_rank": (0.0, 8.0), "head_mix": (0.0, 15.0)}
+
+
 class RandomSource:
     """A tensor source (same interface as ``FolderSource``) that makes tensors up."""
 
@@ -103,8 +108,9 @@ class RandomSource:
 
     def read(self, name: str) -> torch.Tensor:
         d = self._decls[name]
-        return random_tensor(tuple(d.shape), tensor_key(self.seed, name), self.std,
-                             1.0 if d.role == "norm" else 0.0, self._dtype, self.device)
+        offset, widen = ROLE_INIT.get(d.role, (0.0, 1.0))
+        return random_tensor(tuple(d.shape), tensor_key(self.seed, name), self.std * widen,
+                             offset, self._dtype, self.device)
 
 
 def write_model_folder(folder: str, config_json: dict, seed: int, dtype: torch.dtype = torch.bfloat16,
