@@ -56,7 +56,10 @@ def _mixer_spec(c: VizalixConfig, i: int, shapes) -> PartSpec:
         return PartSpec("head_mix_attention", {
             "hidden_size": W, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],
             "value_dim": m["vdim"], "window": m["mask"]["size"], "scale": m["scale"],
-            "softcap": m.get("softcap", 0.0), "head_mix": True, "position": position})
+            "softcap": m.get("softcap", 0.0), "position": position,
+            # every attention layer of the design mixes its heads' scores; a checkpoint header that was read
+            # and lacks the matrix says otherwise
+            "head_mix": shapes is None or f"l{i}.mix.talk" in shapes})
     return PartSpec("mamba2", {
         "hidden_size": W, "num_heads": m["heads"], "head_dim": m["vdim"], "state_size": m["state"],
         "groups": m.get("groups", 1), "norm_groups": m.get("norm_groups", 1), "conv": m["conv"], "eps": c.eps})
