@@ -444,6 +444,204 @@ def run_ours(args):
     return 0
 
 
+# --------------------------------------------------------------------------- #
+# --vizalix: the Vizalix design beside the closest built-in model at equal sizes
+# --------------------------------------------------------------------------- #
+VIZALIX_SIZES = {          # width, heads, key/value heads, head size, feed-forward width
+    "0.3b": (1024, 8, 4, 128, 2816),
+    "1b": (2048, 16, 4, 128, 5632),
+    "3b": (3072, 24, 8, 128, 8192),
+}
+
+
+def vizalix_config(size, window, vocab):
+    W, H, G, d, ff = VIZALIX_SIZES[size]
+    mlp = {"kind": "dense", "ff": ff}
+    delta = {"type": "channel_delta", "mlp": mlp,
+             "mixer": {"heads": H, "kv_heads": H, "dim": d, "vdim": d, "conv": 4, "decay_rank": 64, "gate_rank": 64}}
+    attn = {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "mask": {"size": window}, "scale": d ** -0.5,
+                      "softcap": 30.0, "rot": {"base": 250000.0, "dims": d // 2,
+                                               "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    mamba = {"type": "mamba2", "mlp": mlp,
+             "mixer": {"heads": 2 * H, "vdim": d // 2, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}}
+    return {"architecture": "Vizalix", "vocab": vocab, "width": W, "norm": {"eps": 1e-6},
+            "layers": [delta, attn, mamba, delta, attn, mamba], "loop": {"start": 1, "stop": 5, "times": 2}}
+
+
+def dense_twin_config(size, window, vocab, layer_runs):
+    """The closest built-in model: Qwen2-MoE with every layer dense (grouped-query attention behind the same
+    window, SwiGLU feed-forward), as many layers as the Vizalix model has layer runs, the same widths."""
+    W, H, G, d, ff = VIZALIX_SIZES[size]
+    return dict(A27B, vocab_size=vocab, hidden_size=W, intermediate_size=ff, num_hidden_layers=layer_runs,
+                num_attention_heads=H, num_key_value_heads=G, head_dim=d, num_experts=4, num_experts_per_tok=2,
+                moe_intermediate_size=64, shared_expert_intermediate_size=0, mlp_only_layers=list(range(layer_runs)),
+                use_sliding_window=True, sliding_window=window, max_window_layers=0, max_position_embeddings=1 << 20)
+
+
+def _kernel_table(step, steps=2):
+    """Device time per kernel of ``steps`` calls of ``step`` (CUPTI through torch.profiler), per call."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+    agg = collections.OrderedDict()
+    for e in prof.events():
+        if e.device_type != torch.autograd.DeviceType.CUDA or not e.name or "Memcpy" in e.name or "Memset" in e.name:
+            continue
+        name = e.name.split("<")[0].split("(")[0].replace("void ", "").replace("mi::", "")[:60]
+        a = agg.setdefault(name, [0, 0.0])
+        a[0] += 1
+        a[1] += e.time_range.end - e.time_range.start
+    return {n: {"launches": c // steps, "us": round(d / steps, 1)} for n, (c, d) in
+            sorted(agg.items(), key=lambda kv: -kv[1][1])}
+
+
+def _vizalix_kernel_work(cfg, T, B, ctx, decode):
+    """Algorithmic bytes and floating-point operations of the design's own kernels for one step over all
+    layer runs (prefill of T tokens of one request, or a decode step of B requests at context ctx)."""
+    runs = {0: 1, 1: 2, 2: 2, 3: 2, 4: 2, 5: 1}
+    rows = B if decode else T
+    W = cfg["width"]
+    out = {}
+
+    def add(name, by, fl):
+        a = out.setdefault(name, [0.0, 0.0])
+        a[0] += by
+        a[1] += fl
+    for i, L in enumerate(cfg["layers"]):
+        n, m = runs[i], L["mixer"]
+        if L["type"] == "channel_delta":
+            H, d, e = m["heads"], m["dim"], m["vdim"]
+            ch = 2 * m["kv_heads"] * d + H * e
+            state = (B if decode else 1) * H * d * e * 4 * 2
+            add("delta_scan_kernel", n * (rows * (ch + H * d + H + H * e) * 4 + state), n * rows * H * d * e * 6.0)
+            add("causal_conv_silu_kernel", n * rows * ch * 8, n * rows * ch * 8.0)
+            add("gated_group_rmsnorm_kernel", n * rows * H * e * (4 + 4 + 2), 0)
+        elif L["type"] == "mamba2":
+            H, P, N = m["heads"], m["vdim"], m["state"]
+            ch = H * P + 2 * N
+            state = (B if decode else 1) * H * N * P * 4 * 2
+            add("ssd_scan_kernel", n * (rows * (ch + H + H * P) * 4 + state), n * rows * H * N * P * 4.0)
+            add("causal_conv_silu_kernel", n * rows * ch * 8, n * rows * ch * 8.0)
+            add("gated_group_rmsnorm_kernel", n * rows * H * P * (4 + 4 + 2), 0)
+        else:
+            H, G, d, e, win = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
+            if decode:
+                keys = min(ctx, win)
+                pairs = B * keys
+                by = B * keys * G * (d + e) * 2 + B * H * (d + e) * 2
+            else:
+                pairs = sum(min(t + 1, win) for t in range(T))
+                by = T * (H * (d + e) + G * (d + e)) * 2
+            add("attn_mix_kernel", n * by, n * pairs * H * (2.0 * d + 2.0 * e + 2.0 * H))
+            add("rope_store_kernel", n * rows * (H * d + G * (d + e)) * 6, 0)
+        add("add2_rmsnorm_scalar_kernel", n * rows * W * (4 * 4 + 2 * 2), 0)
+        add("geglu_tanh_kernel", n * rows * L["mlp"]["ff"] * 6, 0)
+    return out
+
+
+def run_vizalix(args):
+    """``--vizalix``: prefill and decode throughput of the Vizalix design at sizes that resemble a real
+    model's layers (random weights), beside the closest built-in model (an all-dense Qwen2-MoE with the same
+    width, heads, window, feed-forward width and as many layers as Vizalix has layer runs), with the device
+    time of every kernel of one step of each and, for the design's own kernels, the share of the roofline
+    (the slower of algorithmic bytes over the measured copy bandwidth and operations over the measured bf16
+    product rate).  Prints one JSON line; the default workload of this file is not touched."""
+    import torch
+    from mini_infer_b200.engine.defaults import DEFAULT_PAGE_SIZE
+    from mini_infer_b200.engine.loading import random_model
+    from mini_infer_b200.engine.step import ModelRunner, StepEntry
+
+    pk = peaks()
+    T, B, ctx, page = args.prompt_len, args.batch, args.prompt_len, DEFAULT_PAGE_SIZE
+    vocab, window = 32000, args.vizalix_window
+    result = {"metric": "vizalix_vs_dense_twin", "prompt_len": T, "decode_batch": B, "decode_context": ctx,
+              "window": window, "dtype": "bf16", "data": "synthetic", "peaks": pk, "sizes": {}}
+    sampler = ClockSampler()
+    sampler.start()
+    for size in [x for x in args.vizalix.split(",") if x]:
+        entry = {}
+        vz = vizalix_config(size, window, vocab)
+        for which, cfg in (("vizalix", vz), ("dense_twin", dense_twin_config(size, window, vocab, 10))):
+            model, rt = random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0")
+            runner = ModelRunner(model, rt, page_size=page, num_pages=(B + 1) * (-(-(ctx + 512) // page)) + 8,
+                                 max_requests=max(B, 2), max_tokens_per_step=max(T, B), max_context=ctx + 512,
+                                 cuda_graphs=not args.eager)
+            g = torch.Generator().manual_seed(args.seed)
+            V = cfg.get("vocab", cfg.get("vocab_size"))
+
+            def prompt():
+                return torch.randint(0, V, (T,), generator=g).tolist()
+
+            def timed(fn, reps):
+                best = 1e30
+                for _ in range(reps):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    a.record()
+                    fn()
+                    b.record()
+                    torch.cuda.synchronize()
+                    best = min(best, a.elapsed_time(b))
+                return best
+
+            count = {"n": 0}
+
+            def prefill():
+                count["n"] += 1
+                rid = ("p", count["n"])
+                runner.add_request(rid)
+                runner.step([StepEntry(rid, toks, [T - 1])])
+                runner.release(rid)
+            toks = prompt()
+            for _ in range(max(3, args.warmup)):
+                prefill()
+            pf_ms = timed(prefill, 5)
+            pf_kernels = _kernel_table(prefill)
+            for b in range(B):
+                runner.add_request(b)
+                runner.step([StepEntry(b, prompt(), [])])
+            state = {"toks": [1] * B}
+
+            def decode():
+                res = runner.step([StepEntry(b, [state["toks"][b]], [0]) for b in range(B)])
+                state["last"] = res.logits
+            for _ in range(max(3, args.warmup)):
+                decode()
+
+            def decode_many():
+                for _ in range(args.steps):
+                    decode()
+            dc_ms = timed(decode_many, 2) / args.steps
+            dc_kernels = _kernel_table(decode, 4)
+            entry[which] = {"prefill_tok_s": round(T / (pf_ms / 1e3), 1), "prefill_ms": round(pf_ms, 3),
+                            "decode_tok_s": round(B / (dc_ms / 1e3), 1), "decode_ms_per_step": round(dc_ms, 4),
+                            "params_millions": round(sum(p.numel() for part in model.all_parts() for p in
+                                                         vars(part).values() if isinstance(p, torch.Tensor)
+                                                         and p.dtype == torch.bfloat16) / 1e6, 1),
+                            "prefill_kernels": pf_kernels, "decode_kernels": dc_kernels}
+            if which == "vizalix":
+                for phase, table, dec in (("prefill", pf_kernels, False), ("decode", dc_kernels, True)):
+                    work = _vizalix_kernel_work(cfg, T, B, ctx, dec)
+                    for name, (by, fl) in work.items():
+                        if name in table:
+                            floor_us = max(by / (pk["hbm_gbs"] * 1e9), fl / (pk["bf16_tflops"] * 1e12)) * 1e6
+                            table[name]["roofline_us"] = round(floor_us, 2)
+                            table[name]["frac"] = round(floor_us / max(table[name]["us"], 1e-9), 4)
+            del runner, model
+            torch.cuda.empty_cache()
+        result["sizes"][size] = entry
+    result["clocks"] = sampler.stop()
+    print(json.dumps(result))
+    return 0
+
+
+
 def run_reference(args):
     """The reference arm: Deyu-Kong/mini-infer itself, unmodified, built out of tree for sm_100 by
     ``baseline/build_reference.py`` and driven by ``baseline/reference_bench.cpp`` through its stock path
@@ -573,6 +771,10 @@ def main():
     ap.add_argument("--serving-prompt-min", type=int, default=100)
     ap.add_argument("--serving-prompt-max", type=int, default=2000)
     ap.add_argument("--serving-max-running", type=int, default=64)
+    ap.add_argument("--vizalix", default="", metavar="SIZES",
+                    help="instead of the default workload: the Vizalix design beside the closest built-in model at "
+                         "these sizes (comma-separated, of " + ", ".join(VIZALIX_SIZES) + "), see run_vizalix")
+    ap.add_argument("--vizalix-window", type=int, default=1024, help="attention window of the --vizalix models")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference's program may take")
     ap.add_argument("--reference-prefill-batch", type=int, default=1,
                     help="prompts the reference's scheduler prefills per iteration (its cuBLAS handles, one per "
@@ -590,6 +792,8 @@ def main():
         return run_timeline(args)
     if args.serving > 0:
         return run_serving(args)
+    if args.vizalix:
+        return run_vizalix(args)
     return run_ours(args)
 
 

@@ -1,0 +1,385 @@
+// Head-mixing attention (see attention_mix.cu for the mechanism) on the tensor cores, bfloat16 storage.
+//
+// A block owns 16 consecutive queries of one request with ALL heads: the scores of a (query, key) pair are
+// mixed over the heads before the softmax, so no head can be computed alone.  Per tile of KT keys:
+//   1. K tile of every key/value head into shared memory (16-byte loads)
+//   2. S_h = Q_h K_g^T with mma.sync m16n8k16 (warp w owns heads w, w + 8, ...), scaled, capped, to shared
+//      memory as float
+//   3. V tile over the K tile; meanwhile the mix over heads and the mask, pair by pair, into a second buffer
+//   4. running softmax in the layout of the A fragments (a row's maximum and sum live in a quad of lanes),
+//      O_h += P_h V_g with V fragments fetched by ldmatrix.trans from the row-major tile
+// Steps of one token per request are split over the keys (blocks of 128 keys write a partial maximum, sum
+// and unnormalised output; a merge kernel finishes), since one block per request cannot pull a window of
+// keys from memory fast enough.
+//
+// Built for value sizes 64 and 128, key sizes that are multiples of 16, up to 16 heads of value size 128 or
+// 32 of 64 (the accumulators of all heads of 16 queries must fit the registers of one block); other shapes
+// and the float path take the kernel of attention_mix.cu.
+
+#include "common.cuh"
+
+namespace mi {
+
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* smem_row) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+constexpr int kTcQ = 16;          // queries per block
+constexpr int kTcWarps = 8;
+constexpr int kTcSplitKeys = 128; // keys per block of a split step
+
+template <int HPW, int NT, int KT>      // heads per warp, value size / 8, keys per tile
+__global__ void __launch_bounds__(256, 1)
+attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                   const __nv_bfloat16* __restrict__ v_cache, const float* __restrict__ mix,
+                   const int* __restrict__ block_table, const int* __restrict__ q_start,
+                   const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, int H, int G, int dk, int page_size, int max_pages, int window,
+                   float scale, float cap, int splits) {
+    constexpr int DV = NT * 8;
+    constexpr int SP = KT + 1;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    wait_for_earlier_kernels();
+    const int b = blockIdx.y, qt = blockIdx.x, split = blockIdx.z;
+    const int q0 = q_start[b], q_len = q_start[b + 1] - q0;
+    if (qt * kTcQ >= q_len) return;
+    const int kvl = kv_len[b];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r0 = lane >> 2, c2 = (lane & 3) * 2;
+    const int rep = H / G;
+    const int dkp = dk + 8, dvp = DV + 8;
+    const int kv_stride = dkp > dvp ? dkp : dvp;
+    float* S1 = reinterpret_cast<float*>(smem_raw);                       // [H][16][SP]
+    float* S2 = S1 + H * kTcQ * SP;                                       // [H][16][SP]
+    float* Mx = S2 + H * kTcQ * SP;                                       // [H][H]
+    int* slot_of = reinterpret_cast<int*>(Mx + ((H * H + 3) & ~3));       // [KT]
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(slot_of + KT + ((4 - KT % 4) % 4));   // [H][16][dkp]
+    __nv_bfloat16* KV = Qs + (size_t)H * kTcQ * dkp;                      // [G][KT][kv_stride]
+
+    const int nq = min(kTcQ, q_len - qt * kTcQ);
+    const int p_lo = kvl - q_len + qt * kTcQ;
+    const int p_hi = p_lo + nq - 1;
+
+    // Q tile: rows of 16 bytes
+    const int qchunks = dk / 8;
+    for (int idx = tid; idx < H * kTcQ * qchunks; idx += 256) {
+        const int c8 = idx % qchunks, i = (idx / qchunks) % kTcQ, h = idx / (qchunks * kTcQ);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (i < nq) v = *reinterpret_cast<const uint4*>(q + ((size_t)(q0 + qt * kTcQ + i) * H + h) * dk + c8 * 8);
+        *reinterpret_cast<uint4*>(Qs + ((size_t)h * kTcQ + i) * dkp + c8 * 8) = v;
+    }
+    if (mix) for (int idx = tid; idx < H * H; idx += 256) Mx[idx] = mix[idx];
+
+    float acc[HPW][NT][4];
+    float m_run[HPW][2], l_run[HPW][2];
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        m_run[hh][0] = m_run[hh][1] = -INFINITY;
+        l_run[hh][0] = l_run[hh][1] = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[hh][nt][x] = 0.f;
+    }
+
+    int k_begin = 0;
+    if (window > 0) k_begin = max(0, p_lo - window + 1);
+    k_begin = (k_begin / KT) * KT;
+    int k_end = min(kvl, p_hi + 1);
+    if (splits > 1) {
+        k_begin += split * kTcSplitKeys;
+        k_end = min(k_end, k_begin + kTcSplitKeys);
+    }
+    const int* table = block_table + (size_t)b * max_pages;
+
+    for (int kt = k_begin; kt < k_end; kt += KT) {
+        __syncthreads();
+        if (tid < KT) {
+            const int kj = kt + tid;
+            int s = -1;
+            if (kj < k_end) {
+                const int page = table[kj / page_size];
+                if (page >= 0) s = page * page_size + kj % page_size;
+            }
+            slot_of[tid] = s;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < G * KT * qchunks; idx += 256) {
+            const int c8 = idx % qchunks, j = (idx / qchunks) % KT, g = idx / (qchunks * KT);
+            const int s = slot_of[j];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (s >= 0) {
+                const int page = s / page_size, off = s - page * page_size;
+                v = *reinterpret_cast<const uint4*>(k_cache + (((size_t)page * G + g) * page_size + off) * dk + c8 * 8);
+            }
+            *reinterpret_cast<uint4*>(KV + ((size_t)g * KT + j) * kv_stride + c8 * 8) = v;
+        }
+        __syncthreads();
+        // ---- scores ----
+#pragma unroll
+        for (int hh = 0; hh < HPW; ++hh) {
+            const int h = warp + kTcWarps * hh;
+            if (h < H) {
+                const int g = h / rep;
+                float c[KT / 8][4];
+#pragma unroll
+                for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) c[nt][x] = 0.f;
+                const __nv_bfloat16* qb = Qs + (size_t)h * kTcQ * dkp;
+                const __nv_bfloat16* kb = KV + (size_t)g * KT * kv_stride;
+                for (int ks = 0; ks < dk; ks += 16) {
+                    const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qb + r0 * dkp + ks + c2);
+                    const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qb + (r0 + 8) * dkp + ks + c2);
+                    const uint32_t a2 = *reinterpret_cast<const uint32_t*>(qb + r0 * dkp + ks + 8 + c2);
+                    const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qb + (r0 + 8) * dkp + ks + 8 + c2);
+#pragma unroll
+                    for (int nt = 0; nt < KT / 8; ++nt) {
+                        const __nv_bfloat16* kr = kb + (size_t)(nt * 8 + r0) * kv_stride + ks + c2;
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + 8);
+                        mma_bf16_16816(c[nt], a0, a1, a2, a3, b0, b1);
+                    }
+                }
+                float* sb = S1 + (size_t)h * kTcQ * SP;
+#pragma unroll
+                for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        float s = c[nt][x] * scale;
+                        if (cap > 0.f) s = cap * tanhf(s / cap);
+                        sb[(r0 + (x >> 1) * 8) * SP + nt * 8 + c2 + (x & 1)] = s;
+                    }
+            }
+        }
+        __syncthreads();
+        // ---- V over K; mix and mask ----
+        constexpr int vchunks = DV / 8;
+        for (int idx = tid; idx < G * KT * vchunks; idx += 256) {
+            const int c8 = idx % vchunks, j = (idx / vchunks) % KT, g = idx / (vchunks * KT);
+            const int s = slot_of[j];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (s >= 0) {
+                const int page = s / page_size, off = s - page * page_size;
+                v = *reinterpret_cast<const uint4*>(v_cache + (((size_t)page * G + g) * page_size + off) * DV + c8 * 8);
+            }
+            *reinterpret_cast<uint4*>(KV + ((size_t)g * KT + j) * kv_stride + c8 * 8) = v;
+        }
+        for (int e = tid; e < kTcQ * KT; e += 256) {
+            const int i = e / KT, j = e - i * KT;
+            const int kj = kt + j, pos = p_lo + i;
+            const bool vis = i < nq && kj <= pos && (window == 0 || kj > pos - window) && slot_of[j] >= 0;
+            for (int h = 0; h < H; ++h) {
+                float s;
+                if (mix) {
+                    s = 0.f;
+                    for (int g = 0; g < H; ++g) s += Mx[h * H + g] * S1[(g * kTcQ + i) * SP + j];
+                } else {
+                    s = S1[(h * kTcQ + i) * SP + j];
+                }
+                S2[(h * kTcQ + i) * SP + j] = vis ? s : -INFINITY;
+            }
+        }
+        __syncthreads();
+        // ---- softmax and P.V ----
+#pragma unroll
+        for (int hh = 0; hh < HPW; ++hh) {
+            const int h = warp + kTcWarps * hh;
+            if (h < H) {
+                const int g = h / rep;
+                const float* sb = S2 + (size_t)h * kTcQ * SP;
+                float p[KT / 8][4];
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int nt = 0; nt < KT / 8; ++nt) {
+                    p[nt][0] = sb[r0 * SP + nt * 8 + c2];
+                    p[nt][1] = sb[r0 * SP + nt * 8 + c2 + 1];
+                    p[nt][2] = sb[(r0 + 8) * SP + nt * 8 + c2];
+                    p[nt][3] = sb[(r0 + 8) * SP + nt * 8 + c2 + 1];
+                    mx0 = fmaxf(mx0, fmaxf(p[nt][0], p[nt][1]));
+                    mx1 = fmaxf(mx1, fmaxf(p[nt][2], p[nt][3]));
+                }
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m_run[hh][0], mx0), mn1 = fmaxf(m_run[hh][1], mx1);
+                const float al0 = mn0 == -INFINITY ? 1.f : expf(m_run[hh][0] - mn0);
+                const float al1 = mn1 == -INFINITY ? 1.f : expf(m_run[hh][1] - mn1);
+                float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                for (int nt = 0; nt < KT / 8; ++nt) {
+                    p[nt][0] = mn0 == -INFINITY ? 0.f : expf(p[nt][0] - mn0);
+                    p[nt][1] = mn0 == -INFINITY ? 0.f : expf(p[nt][1] - mn0);
+                    p[nt][2] = mn1 == -INFINITY ? 0.f : expf(p[nt][2] - mn1);
+                    p[nt][3] = mn1 == -INFINITY ? 0.f : expf(p[nt][3] - mn1);
+                    s0 += p[nt][0] + p[nt][1];
+                    s1 += p[nt][2] + p[nt][3];
+                }
+                l_run[hh][0] = l_run[hh][0] * al0 + s0;     // a lane's share; the quad is summed at the end
+                l_run[hh][1] = l_run[hh][1] * al1 + s1;
+                m_run[hh][0] = mn0;
+                m_run[hh][1] = mn1;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    acc[hh][nt][0] *= al0; acc[hh][nt][1] *= al0;
+                    acc[hh][nt][2] *= al1; acc[hh][nt][3] *= al1;
+                }
+                const __nv_bfloat16* vb = KV + (size_t)g * KT * kv_stride;
+#pragma unroll
+                for (int kk = 0; kk < KT / 16; ++kk) {
+                    const uint32_t a0 = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+                    const uint32_t a1 = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+                    const uint32_t a2 = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+                    const uint32_t a3 = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+                    const __nv_bfloat16* vrow = vb + (size_t)(kk * 16 + (lane & 15)) * kv_stride;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        uint32_t b0, b1;
+                        ldmatrix_x2_trans(b0, b1, vrow + nt * 8);
+                        mma_bf16_16816(acc[hh][nt], a0, a1, a2, a3, b0, b1);
+                    }
+                }
+            }
+        }
+    }
+    // ---- results ----
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        const int h = warp + kTcWarps * hh;
+        if (h < H) {
+            float l0 = l_run[hh][0], l1 = l_run[hh][1];
+            l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+            if (splits > 1) {
+                // one query per request: row 0 of the tile
+                if (r0 == 0) {
+                    const size_t base = ((size_t)b * splits + split) * H + h;
+                    float* po = part_o + base * DV;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        po[nt * 8 + c2] = acc[hh][nt][0];
+                        po[nt * 8 + c2 + 1] = acc[hh][nt][1];
+                    }
+                    if ((lane & 3) == 0) { part_ml[base * 2] = m_run[hh][0]; part_ml[base * 2 + 1] = l0; }
+                }
+            } else {
+                const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    if (r0 < nq)
+                        *reinterpret_cast<uint32_t*>(out + ((size_t)(q0 + qt * kTcQ + r0) * H + h) * DV + nt * 8 + c2) =
+                            pack_bf16(acc[hh][nt][0] * i0, acc[hh][nt][1] * i0);
+                    if (r0 + 8 < nq)
+                        *reinterpret_cast<uint32_t*>(out + ((size_t)(q0 + qt * kTcQ + r0 + 8) * H + h) * DV + nt * 8 + c2) =
+                            pack_bf16(acc[hh][nt][2] * i1, acc[hh][nt][3] * i1);
+                }
+            }
+        }
+    }
+}
+
+// out[b, h, :] from the partial results of the splits, in split order
+__global__ void __launch_bounds__(128)
+attn_mix_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                      const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, int H, int DV, int splits) {
+    wait_for_earlier_kernels();
+    const int b = blockIdx.y, h = blockIdx.x;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(((size_t)b * splits + s) * H + h) * 2]);
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const size_t base = ((size_t)b * splits + s) * H + h;
+        const float ms = part_ml[base * 2];
+        if (ms != -INFINITY) l += part_ml[base * 2 + 1] * expf(ms - m);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const int row = q_start[b];
+    for (int c = threadIdx.x; c < DV; c += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const size_t base = ((size_t)b * splits + s) * H + h;
+            const float ms = part_ml[base * 2];
+            if (ms != -INFINITY) o += part_o[base * DV + c] * expf(ms - m);
+        }
+        out[((size_t)row * H + h) * DV + c] = __float2bfloat16_rn(o * inv);
+    }
+}
+
+static size_t tc_smem(int H, int G, int dk, int dv, int kt) {
+    const int dkp = dk + 8, dvp = dv + 8;
+    const int kvs = dkp > dvp ? dkp : dvp;
+    return (size_t)2 * H * kTcQ * (kt + 1) * 4 + (size_t)((H * H + 3) & ~3) * 4 + (size_t)(kt + 4) * 4 + (size_t)H * kTcQ * dkp * 2 +
+           (size_t)G * kt * kvs * 2 + 16;
+}
+
+// keys per tile for a model's sizes (0: the shape is not taken)
+static int tc_plan(int H, int G, int dk, int dv) {
+    if (H < 1 || G < 1 || H % G || dk % 16 || dk < 16 || dk > 256 || (dv != 64 && dv != 128)) return 0;
+    const int hpw = (H + kTcWarps - 1) / kTcWarps;
+    if (hpw * (dv / 8) > 32) return 0;
+    if (tc_smem(H, G, dk, dv, 32) <= 220 * 1024) return 32;
+    if (tc_smem(H, G, dk, dv, 16) <= 220 * 1024) return 16;
+    return 0;
+}
+
+}  // namespace mi
+
+using namespace mi;
+
+extern "C" {
+
+int mi_attn_mix_tc_supported(int H, int G, int dk, int dv) { return tc_plan(H, G, dk, dv) > 0; }
+
+// splits a step of single tokens is cut into, given the longest span of keys a query can see
+int mi_attn_mix_tc_splits(int span) { return (span + kTcSplitKeys - 1) / kTcSplitKeys + 1; }
+
+int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, const float* mix, const int* block_table,
+                   const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
+                   int max_q_len, int H, int G, int dk, int dv, int page_size, int max_pages, int window,
+                   float scale, float cap, int splits, cudaStream_t stream) {
+    if (B <= 0 || max_q_len <= 0) return kOk;
+    const int kt = tc_plan(H, G, dk, dv);
+    if (!kt) {
+        set_last_error("mixed-head attention (tensor cores): heads %d/%d, key size %d, value size %d are not taken", H, G, dk, dv);
+        return kBadShape;
+    }
+    if (splits < 1 || (splits > 1 && (max_q_len != 1 || !part_o || !part_ml)) || B > 65535 || splits > 65535) {
+        set_last_error("mixed-head attention (tensor cores): %d splits with portions of %d tokens, batch %d", splits, max_q_len, B);
+        return kBadShape;
+    }
+    const int hpw = (H + kTcWarps - 1) / kTcWarps;
+    const size_t smem = tc_smem(H, G, dk, dv, kt);
+    const dim3 grid((max_q_len + kTcQ - 1) / kTcQ, B, splits);
+#define MI_TC_LAUNCH(HPW, NT, KT)                                                                               \
+    do {                                                                                                        \
+        cudaFuncSetAttribute(attn_mix_tc_kernel<HPW, NT, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_dependent(attn_mix_tc_kernel<HPW, NT, KT>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)q, \
+                         (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, mix, block_table, q_start, \
+                         kv_len, (__nv_bfloat16*)out, part_o, part_ml, H, G, dk, page_size, max_pages, window,  \
+                         scale, cap, splits);                                                                   \
+    } while (0)
+#define MI_TC_KT(HPW, NT) do { if (kt == 32) MI_TC_LAUNCH(HPW, NT, 32); else MI_TC_LAUNCH(HPW, NT, 16); } while (0)
+    if (dv == 128) {
+        if (hpw == 1) MI_TC_KT(1, 16); else MI_TC_KT(2, 16);
+    } else {
+        if (hpw == 1) MI_TC_KT(1, 8); else if (hpw == 2) MI_TC_KT(2, 8); else MI_TC_KT(4, 8);
+    }
+#undef MI_TC_KT
+#undef MI_TC_LAUNCH
+    int launched = 1;
+    if (splits > 1) {
+        launch_dependent(attn_mix_merge_kernel, dim3(H, B), dim3(128), 0, stream, (const float*)part_o,
+                         (const float*)part_ml, q_start, (__nv_bfloat16*)out, H, dv, splits);
+        launched = 2;
+    }
+    return finish_launch("attn_mix_tc", launched);
+}
+
+}  // extern "C"

@@ -9,8 +9,8 @@
 //   gated_group_rmsnorm  RMS norm over equal groups of a row, with a gate before (silu) or after (sigmoid) it
 //
 // The recurrences walk a request's tokens of the step in order, one block per (request, head, slice of
-// 32 value columns); a thread holds a quarter of one column of S in registers, so that the products with
-// k_t and q_t (or C_t) are sums inside a thread and over four neighbouring lanes.  What a token needs
+// 16 value columns); a thread holds an eighth of one column of S in registers, so that the products with
+// k_t and q_t (or C_t) are sums inside a thread and over eight neighbouring lanes.  What a token needs
 // besides S (unit vectors, decays, step sizes) is prepared for 8 tokens at a time by the whole block.
 // All arithmetic is float, whatever the storage type of the activations; the state is float.  The order
 // of the additions of a token depends on nothing but the sizes of the model, so a prompt cut into
@@ -83,54 +83,65 @@ conv_state_update_kernel(const float* __restrict__ x, int ldx, float* __restrict
 }
 
 // ---------------------------------------------------------------------------
-// The two recurrences.  Block = 128 threads = 32 value columns x 4 lanes; lane r of a column holds the
-// rows r, r+4, r+8, ... of that column (RP of them).  Tokens are prepared 8 at a time.
+// The two recurrences.  Block = 128 threads = 16 value columns x 8 lanes; lane r of a column holds, of that
+// column of S, the rows 4 (r + 8 m) .. 4 (r + 8 m) + 3 for m = 0 .. RP/4 - 1 (RP rows in all), so that the
+// vectors a token brings are read from shared memory sixteen bytes at a time and a sum over rows is four
+// independent chains inside a thread, then three exchanges among the eight lanes.  Tokens are prepared 8 at
+// a time by the whole block; a chunk's results go out together.
 // ---------------------------------------------------------------------------
-constexpr int kScanCols = 32;
-constexpr int kScanLanes = 4;
+constexpr int kScanLanes = 8;
+constexpr int kScanCols = 128 / kScanLanes;
 constexpr int kScanChunk = 8;
 
-__device__ __forceinline__ float quad_sum(float v) {
+__device__ __forceinline__ float lanes_sum(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
     return v;
 }
+
+// row of S that element (m, x) of lane r holds
+__device__ __forceinline__ int scan_row(int r, int m, int x) { return 4 * (r + kScanLanes * m) + x; }
 
 // qkv: [T, ld_qkv] float, q heads at column 0 (G x d), k heads at G*d, v heads at 2*G*d (H x dv), all after
 // the convolution; beta_raw: [T, ld_beta] at its own pointer (H columns); a_raw: [T, ld_a] (H x d columns,
 // before dt_bias and softplus).  out: [T, H*dv] float.
 template <int RP>
-__global__ void __launch_bounds__(kScanCols * kScanLanes)
+__global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __restrict__ beta_raw, int ld_beta,
                   const float* __restrict__ a_raw, int ld_a, const float* __restrict__ a_log,
                   const float* __restrict__ dt_bias, float* __restrict__ state, int64_t state_stride,
                   const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ out,
                   int H, int G, int d, int dv, float q_scale) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     constexpr int DP = RP * kScanLanes;                 // rows, padded
+    constexpr int MV = RP / 4;
     float* qs = sm;                                     // [chunk][DP] unit q times q_scale
     float* ks = qs + kScanChunk * DP;                   // [chunk][DP] unit k
     float* gs = ks + kScanChunk * DP;                   // [chunk][DP] decay
-    float* vs = gs + kScanChunk * DP;                   // [chunk][32] v of this slice
-    float* bs = vs + kScanChunk * kScanCols;            // [chunk] beta
+    float* vs = gs + kScanChunk * DP;                   // [chunk][16] v of this slice
+    float* os = vs + kScanChunk * kScanCols;            // [chunk][16] results of the chunk
+    float* bs = os + kScanChunk * kScanCols;            // [chunk] beta
     wait_for_earlier_kernels();
     const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * kScanCols;
     const int hk = h / (H / G);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = tid & (kScanLanes - 1), col = col0 + (tid >> 2);
+    const int r = tid & (kScanLanes - 1), lc = tid / kScanLanes, col = col0 + lc;
     const bool col_ok = col < dv;
     const int q0 = q_start[b], n = q_start[b + 1] - q0;
     float* S = state + (int64_t)state_slot[b] * state_stride + (int64_t)h * d * dv;
     float s[RP];
 #pragma unroll
-    for (int m = 0; m < RP; ++m) {
-        const int i = r + kScanLanes * m;
-        s[m] = (col_ok && i < d) ? S[(int64_t)i * dv + col] : 0.f;
-    }
+    for (int m = 0; m < MV; ++m)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = scan_row(r, m, x);
+            s[4 * m + x] = (col_ok && i < d) ? S[(int64_t)i * dv + col] : 0.f;
+        }
     const float neg_a = -expf(a_log[h]);
     for (int c0 = 0; c0 < n; c0 += kScanChunk) {
         const int nc = min(kScanChunk, n - c0);
-        __syncthreads();                                // the chunk before has been consumed
+        __syncthreads();                                // the chunk before has been consumed and written out
         // a warp prepares tokens warp, warp + 4 of the chunk
         for (int tt = warp; tt < nc; tt += 4) {
             const int64_t t = q0 + c0 + tt;
@@ -151,70 +162,83 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __rest
                 }
                 qs[tt * DP + i] = qv; ks[tt * DP + i] = kv; gs[tt * DP + i] = gv;
             }
-            const int cc = col0 + lane;
-            vs[tt * kScanCols + lane] = cc < dv ? qkv[t * ld_qkv + (int64_t)2 * G * d + (int64_t)h * dv + cc] : 0.f;
+            if (lane < kScanCols) {
+                const int cc = col0 + lane;
+                vs[tt * kScanCols + lane] = cc < dv ? qkv[t * ld_qkv + (int64_t)2 * G * d + (int64_t)h * dv + cc] : 0.f;
+            }
             if (lane == 0) bs[tt] = sigmoid_f(beta_raw[t * ld_beta + h]);
         }
         __syncthreads();
         for (int tt = 0; tt < nc; ++tt) {
-            const float* kq = ks + tt * DP;
-            const float* gq = gs + tt * DP;
-            const float* qq = qs + tt * DP;
-            float acc = 0.f;
+            const float4* kq = reinterpret_cast<const float4*>(ks + tt * DP);
+            const float4* gq = reinterpret_cast<const float4*>(gs + tt * DP);
+            const float4* qq = reinterpret_cast<const float4*>(qs + tt * DP);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int m = 0; m < RP; ++m) {
-                const int i = r + kScanLanes * m;
-                s[m] *= gq[i];
-                acc += s[m] * kq[i];
+            for (int m = 0; m < MV; ++m) {
+                const float4 g4 = gq[r + kScanLanes * m], k4 = kq[r + kScanLanes * m];
+                s[4 * m] *= g4.x; s[4 * m + 1] *= g4.y; s[4 * m + 2] *= g4.z; s[4 * m + 3] *= g4.w;
+                a0 += s[4 * m] * k4.x; a1 += s[4 * m + 1] * k4.y; a2 += s[4 * m + 2] * k4.z; a3 += s[4 * m + 3] * k4.w;
             }
-            acc = quad_sum(acc);
-            const float u = bs[tt] * (vs[tt * kScanCols + (tid >> 2)] - acc);
-            float o = 0.f;
+            const float acc = lanes_sum((a0 + a1) + (a2 + a3));
+            const float u = bs[tt] * (vs[tt * kScanCols + lc] - acc);
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-            for (int m = 0; m < RP; ++m) {
-                const int i = r + kScanLanes * m;
-                s[m] += kq[i] * u;
-                o += s[m] * qq[i];
+            for (int m = 0; m < MV; ++m) {
+                const float4 k4 = kq[r + kScanLanes * m], q4 = qq[r + kScanLanes * m];
+                s[4 * m] += k4.x * u; s[4 * m + 1] += k4.y * u; s[4 * m + 2] += k4.z * u; s[4 * m + 3] += k4.w * u;
+                o0 += s[4 * m] * q4.x; o1 += s[4 * m + 1] * q4.y; o2 += s[4 * m + 2] * q4.z; o3 += s[4 * m + 3] * q4.w;
             }
-            o = quad_sum(o);
-            if (r == 0 && col_ok) out[(int64_t)(q0 + c0 + tt) * H * dv + (int64_t)h * dv + col] = o;
+            const float o = lanes_sum((o0 + o1) + (o2 + o3));
+            if (r == 0) os[tt * kScanCols + lc] = o;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nc * kScanCols; idx += 128) {
+            const int tt = idx / kScanCols, c = col0 + idx % kScanCols;
+            if (c < dv) out[(int64_t)(q0 + c0 + tt) * H * dv + (int64_t)h * dv + c] = os[idx];
         }
     }
 #pragma unroll
-    for (int m = 0; m < RP; ++m) {
-        const int i = r + kScanLanes * m;
-        if (col_ok && i < d) S[(int64_t)i * dv + col] = s[m];
-    }
+    for (int m = 0; m < MV; ++m)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = scan_row(r, m, x);
+            if (col_ok && i < d) S[(int64_t)i * dv + col] = s[4 * m + x];
+        }
 }
 
 // xbc: [T, ld_x] float after the convolution: x heads at column 0 (H x P), B groups at H*P (G x N), C groups
 // at H*P + G*N; dt_raw: [T, ld_dt] (H columns, before dt_bias and softplus).  out: [T, H*P] float.
 template <int RP>
-__global__ void __launch_bounds__(kScanCols * kScanLanes)
+__global__ void __launch_bounds__(128)
 ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict__ dt_raw, int ld_dt,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                 float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
                 const int* __restrict__ state_slot, float* __restrict__ out, int H, int G, int N, int P) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     constexpr int NP = RP * kScanLanes;
+    constexpr int MV = RP / 4;
     float* Bs = sm;                                     // [chunk][NP] dt * B
     float* Cs = Bs + kScanChunk * NP;                   // [chunk][NP]
-    float* xs = Cs + kScanChunk * NP;                   // [chunk][32]
-    float* as = xs + kScanChunk * kScanCols;            // [chunk] decay
+    float* xs = Cs + kScanChunk * NP;                   // [chunk][16]
+    float* os = xs + kScanChunk * kScanCols;            // [chunk][16]
+    float* as = os + kScanChunk * kScanCols;            // [chunk] decay
     wait_for_earlier_kernels();
     const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * kScanCols;
     const int g = h / (H / G);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r = tid & (kScanLanes - 1), col = col0 + (tid >> 2);
+    const int r = tid & (kScanLanes - 1), lc = tid / kScanLanes, col = col0 + lc;
     const bool col_ok = col < P;
     const int q0 = q_start[b], n = q_start[b + 1] - q0;
     float* S = state + (int64_t)state_slot[b] * state_stride + (int64_t)h * N * P;
     float s[RP];
 #pragma unroll
-    for (int m = 0; m < RP; ++m) {
-        const int i = r + kScanLanes * m;
-        s[m] = (col_ok && i < N) ? S[(int64_t)i * P + col] : 0.f;
-    }
+    for (int m = 0; m < MV; ++m)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = scan_row(r, m, x);
+            s[4 * m + x] = (col_ok && i < N) ? S[(int64_t)i * P + col] : 0.f;
+        }
     const float neg_a = -expf(a_log[h]);
     const float dskip = d_skip[h];
     const float bias = dt_bias[h];
@@ -230,31 +254,41 @@ ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
                 Bs[tt * NP + i] = i < N ? dt * brow[i] : 0.f;
                 Cs[tt * NP + i] = i < N ? crow[i] : 0.f;
             }
-            const int cc = col0 + lane;
-            xs[tt * kScanCols + lane] = cc < P ? xbc[t * ld_x + (int64_t)h * P + cc] : 0.f;
+            if (lane < kScanCols) {
+                const int cc = col0 + lane;
+                xs[tt * kScanCols + lane] = cc < P ? xbc[t * ld_x + (int64_t)h * P + cc] : 0.f;
+            }
             if (lane == 0) as[tt] = expf(neg_a * dt);
         }
         __syncthreads();
         for (int tt = 0; tt < nc; ++tt) {
-            const float* Bq = Bs + tt * NP;
-            const float* Cq = Cs + tt * NP;
-            const float a = as[tt], xv = xs[tt * kScanCols + (tid >> 2)];
-            float y = 0.f;
+            const float4* Bq = reinterpret_cast<const float4*>(Bs + tt * NP);
+            const float4* Cq = reinterpret_cast<const float4*>(Cs + tt * NP);
+            const float a = as[tt], xv = xs[tt * kScanCols + lc];
+            float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
 #pragma unroll
-            for (int m = 0; m < RP; ++m) {
-                const int i = r + kScanLanes * m;
-                s[m] = a * s[m] + Bq[i] * xv;
-                y += s[m] * Cq[i];
+            for (int m = 0; m < MV; ++m) {
+                const float4 b4 = Bq[r + kScanLanes * m], c4 = Cq[r + kScanLanes * m];
+                s[4 * m] = a * s[4 * m] + b4.x * xv; s[4 * m + 1] = a * s[4 * m + 1] + b4.y * xv;
+                s[4 * m + 2] = a * s[4 * m + 2] + b4.z * xv; s[4 * m + 3] = a * s[4 * m + 3] + b4.w * xv;
+                y0 += s[4 * m] * c4.x; y1 += s[4 * m + 1] * c4.y; y2 += s[4 * m + 2] * c4.z; y3 += s[4 * m + 3] * c4.w;
             }
-            y = quad_sum(y);
-            if (r == 0 && col_ok) out[(int64_t)(q0 + c0 + tt) * H * P + (int64_t)h * P + col] = y + dskip * xv;
+            const float y = lanes_sum((y0 + y1) + (y2 + y3));
+            if (r == 0) os[tt * kScanCols + lc] = y + dskip * xv;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < nc * kScanCols; idx += 128) {
+            const int tt = idx / kScanCols, c = col0 + idx % kScanCols;
+            if (c < P) out[(int64_t)(q0 + c0 + tt) * H * P + (int64_t)h * P + c] = os[idx];
         }
     }
 #pragma unroll
-    for (int m = 0; m < RP; ++m) {
-        const int i = r + kScanLanes * m;
-        if (col_ok && i < N) S[(int64_t)i * P + col] = s[m];
-    }
+    for (int m = 0; m < MV; ++m)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int i = scan_row(r, m, x);
+            if (col_ok && i < N) S[(int64_t)i * P + col] = s[4 * m + x];
+        }
 }
 
 // ---------------------------------------------------------------------------
@@ -322,9 +356,9 @@ int mi_causal_conv_silu(const float* x, int ldx, const void* w, const void* bias
 
 #define MI_SCAN_DISPATCH(rows, ...)                                                     \
     do {                                                                                \
-        if ((rows) <= 64) { constexpr int RP = 16; __VA_ARGS__; }                       \
-        else if ((rows) <= 128) { constexpr int RP = 32; __VA_ARGS__; }                 \
-        else { constexpr int RP = 64; __VA_ARGS__; }                                    \
+        if ((rows) <= 64) { constexpr int RP = 8; __VA_ARGS__; }                        \
+        else if ((rows) <= 128) { constexpr int RP = 16; __VA_ARGS__; }                 \
+        else { constexpr int RP = 32; __VA_ARGS__; }                                    \
     } while (0)
 
 int mi_delta_scan(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
@@ -337,8 +371,8 @@ int mi_delta_scan(const float* qkv, int ld_qkv, const float* beta_raw, int ld_be
     if (B > 65535 || H > 65535) { set_last_error("delta rule: batch %d or heads %d exceed the grid limit", B, H); return kBadShape; }
     const dim3 grid((dv + kScanCols - 1) / kScanCols, H, B);
     MI_SCAN_DISPATCH(d, {
-        const size_t smem = sizeof(float) * (kScanChunk * (3 * RP * kScanLanes + kScanCols + 1));
-        launch_dependent(delta_scan_kernel<RP>, grid, dim3(kScanCols * kScanLanes), smem, stream, qkv, ld_qkv,
+        const size_t smem = sizeof(float) * (kScanChunk * (3 * RP * kScanLanes + 2 * kScanCols + 1));
+        launch_dependent(delta_scan_kernel<RP>, grid, dim3(128), smem, stream, qkv, ld_qkv,
                          beta_raw, ld_beta, a_raw, ld_a, a_log, dt_bias, state, state_stride, q_start, state_slot,
                          out, H, G, d, dv, q_scale);
     });
@@ -354,8 +388,8 @@ int mi_ssd_scan(const float* xbc, int ld_x, const float* dt_raw, int ld_dt, cons
     if (B > 65535 || H > 65535) { set_last_error("state-space scan: batch %d or heads %d exceed the grid limit", B, H); return kBadShape; }
     const dim3 grid((P + kScanCols - 1) / kScanCols, H, B);
     MI_SCAN_DISPATCH(N, {
-        const size_t smem = sizeof(float) * (kScanChunk * (2 * RP * kScanLanes + kScanCols + 1));
-        launch_dependent(ssd_scan_kernel<RP>, grid, dim3(kScanCols * kScanLanes), smem, stream, xbc, ld_x, dt_raw,
+        const size_t smem = sizeof(float) * (kScanChunk * (2 * RP * kScanLanes + 2 * kScanCols + 1));
+        launch_dependent(ssd_scan_kernel<RP>, grid, dim3(128), smem, stream, xbc, ld_x, dt_raw,
                          ld_dt, dt_bias, a_log, d_skip, state, state_stride, q_start, state_slot, out, H, G, N, P);
     });
     return finish_launch("ssd_scan");

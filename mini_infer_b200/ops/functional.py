@@ -1138,3 +1138,47 @@ def attention_mix(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                 dk, dv, page_size, max_pages, int(window), float(scale), float(softcap), _stream()),
           "attention_mix")
     return out
+
+
+def attention_mix_tc_supported(nh: int, nkv: int, dk: int, dv: int) -> bool:
+    """The tensor-core form (bfloat16) takes these sizes."""
+    return bool(library().mi_attn_mix_tc_supported(nh, nkv, dk, dv))
+
+
+def attention_mix_tc_splits(span: int) -> int:
+    """Blocks over the keys that a step of single tokens is cut into when a query sees up to ``span`` keys."""
+    return int(library().mi_attn_mix_tc_splits(int(span)))
+
+
+def attention_mix_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, mix: Optional[torch.Tensor],
+                     block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int,
+                     window: int, scale: float, softcap: float, splits: int = 1,
+                     part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`attention_mix` on the tensor cores (bfloat16).  ``splits > 1`` (steps of one token per request
+    only): the keys of a request are cut into ``splits`` blocks whose partial results go through the float32
+    scratch ``part_o`` (``B * splits * nh * dv``) and ``part_ml`` (``B * splits * nh * 2``)."""
+    _chk(q, "attention_mix_tc q", BF16)
+    T, nh, dk = q.shape
+    _chk(k_cache, "attention_mix_tc k_cache", BF16, (None, None, None, dk))
+    _, nkv, page_size, _ = k_cache.shape
+    _chk(v_cache, "attention_mix_tc v_cache", BF16, (k_cache.shape[0], nkv, page_size, None))
+    dv = v_cache.shape[3]
+    _chk(mix, "attention_mix_tc mix", F32, (nh, nh))
+    _chk(block_table, "attention_mix_tc block_table", I32)
+    B, max_pages = block_table.shape
+    _chk(q_start, "attention_mix_tc q_start", I32, (B + 1,))
+    _chk(kv_len, "attention_mix_tc kv_len", I32, (B,))
+    if splits > 1:
+        _chk(part_o, "attention_mix_tc part_o", F32)
+        _chk(part_ml, "attention_mix_tc part_ml", F32)
+        if part_o is None or part_ml is None or part_o.numel() < B * splits * nh * dv or part_ml.numel() < B * splits * nh * 2:
+            raise ValueError("attention_mix_tc: scratch for the partial results is missing or too small")
+    out = torch.empty(T, nh, dv, dtype=BF16, device=q.device)
+    if DEBUG_BOUNDS:
+        _dbg_batch("attention_mix_tc", q_start, kv_len, block_table, T, k_cache.shape[0], page_size, int(window),
+                   int(max_q_len))
+    check(library().mi_attn_mix_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(mix), _ptr(block_table), _ptr(q_start),
+                                   _ptr(kv_len), _ptr(out), _ptr(part_o), _ptr(part_ml), B, int(max_q_len), nh, nkv, dk,
+                                   dv, page_size, max_pages, int(window), float(scale), float(softcap), int(splits),
+                                   _stream()), "attention_mix_tc")
+    return out

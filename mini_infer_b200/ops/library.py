@@ -53,6 +53,7 @@ _SIGNATURES = {
     "mi_gated_group_rmsnorm": [P, P, I, P, I, I, P, I, I, I, I, I, F, P],
     "mi_rope_store": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "mi_attn_mix": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P],
+    "mi_attn_mix_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, P],
     "mi_add2_rmsnorm_scalar": [P, P, P, P, P, P, P, P, I, I, I, F, P],
     "mi_geglu_tanh": [P, P, I, L, I, P],
     "mi_concat_cast": [P, P, P, P, P, I, I, I, P],
@@ -105,6 +106,10 @@ def library() -> ctypes.CDLL:
     lib.mi_qkv_skinny_supported.restype = c_int
     lib.mi_dense_skinny_max_rows.argtypes = []
     lib.mi_dense_skinny_max_rows.restype = c_int
+    lib.mi_attn_mix_tc_supported.argtypes = [I, I, I, I]
+    lib.mi_attn_mix_tc_supported.restype = c_int
+    lib.mi_attn_mix_tc_splits.argtypes = [I]
+    lib.mi_attn_mix_tc_splits.restype = c_int
     lib.mi_attn_mix_supported.argtypes = [I, I, I, I, I]
     lib.mi_attn_mix_supported.restype = c_int
     lib.mi_attn_decode_split_size.argtypes = []

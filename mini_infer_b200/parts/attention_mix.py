@@ -72,11 +72,23 @@ class HeadMixAttention(Mixer):
             raise ValueError(f"attention: {self.nh} heads of key size {self.dk} and value size {self.dv} "
                              f"are more than one block of the kernel holds")
 
+        # bfloat16: scores and P.V on the tensor cores where the kernel is built for the sizes
+        self._tensor_cores = rt.act == torch.bfloat16 and F.attention_mix_tc_supported(self.nh, self.nkv, self.dk, self.dv)
+
     def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
         F.l2_prefetch(self.w_qkv)
 
     def cache_need(self):
         return KVNeed(self.nkv, self.dk, self.window, value_dim=self.dv)
+
+    def _span(self, max_kv_len: int) -> int:
+        """Most keys a query can see."""
+        return min(self.window, max_kv_len) if self.window > 0 else max_kv_len
+
+    def scratch_need(self, max_requests: int, max_context: int) -> Dict[str, int]:
+        splits = F.attention_mix_tc_splits(self._span(max_context))
+        return {"attn_mix_part_o": max_requests * splits * self.nh * self.dv,
+                "attn_mix_part_ml": max_requests * splits * self.nh * 2}
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheBinding) -> torch.Tensor:
         view = ctx.kv_groups[cache.group]
@@ -84,8 +96,19 @@ class HeadMixAttention(Mixer):
         qkv = linear(x, self.w_qkv, torch.float32)
         q = F.rope_store(qkv, ctx.positions, self.inv_freq, self.rot_dim, view.slot_mapping, kc, vc, self.nh,
                          self.nkv, self.dk, self.dv, view.page_size, self.rt.act)
-        a = F.attention_mix(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
-                            self.window, self.scale, self.softcap)
+        if not self._tensor_cores:
+            # float32: one kernel for every step, sums in an order that the cut of the step cannot change
+            a = F.attention_mix(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
+                                self.window, self.scale, self.softcap)
+        elif ctx.all_decode and "attn_mix_part_o" in ctx.scratch:
+            # one token per request: a block per request could not pull a window of keys fast enough
+            splits = F.attention_mix_tc_splits(self._span(ctx.max_kv_len))
+            a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, 1, self.window,
+                                   self.scale, self.softcap, splits, ctx.scratch["attn_mix_part_o"],
+                                   ctx.scratch["attn_mix_part_ml"])
+        else:
+            a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
+                                   self.window, self.scale, self.softcap)
         return linear(a.view(ctx.num_tokens, self.nh * self.dv), self.w_o, torch.float32)
 
 

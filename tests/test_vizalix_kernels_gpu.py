@@ -360,3 +360,61 @@ def test_rotation_and_cache_write(dtype):
         assert torch.allclose(vc[page, :, off].float().cpu().double(), x[t, (nh + nkv) * dk:].view(nkv, dv), atol=tol)
     assert float(kc[:2].abs().max()) == 0.0 and float(kc[3, :, 0].abs().max()) == 0.0      # slot 12 stayed empty
     assert float(kc[5:].abs().max()) == 0.0 and float(vc[5:].abs().max()) == 0.0
+
+
+def run_attention_tc(q, k, v, talk, window, scale, cap, cuts, page_size=8):
+    """The tensor-core form over a hand-made paged cache; portions of one token go through the split form."""
+    T, H, d = q.shape
+    e = v.shape[2]
+    kc, vc, order = paged(k, v, page_size, 2 * (-(-T // page_size)) + 3, 5, torch.bfloat16)
+    table = i32([order + [-1] * 4])
+    outs, lo = [], 0
+    for n in cuts:
+        kw = {}
+        splits = 1
+        if n == 1:
+            span = min(window, lo + 1) if window else lo + 1
+            splits = F().attention_mix_tc_splits(span)
+            kw = dict(splits=splits, part_o=torch.full((splits * H * e,), 7.0, device=DEV),
+                      part_ml=torch.full((splits * H * 2,), 7.0, device=DEV))
+        got = F().attention_mix_tc(q[lo:lo + n].to(torch.bfloat16).to(DEV).contiguous(), kc, vc,
+                                   None if talk is None else talk.float().to(DEV), table, i32([0, n]), i32([lo + n]), n,
+                                   window, scale, cap or 0.0, **kw)
+        outs.append(got.float().cpu())
+        lo += n
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("H,G,d,e,window", [(16, 4, 64, 128, 40), (8, 4, 128, 128, 300), (4, 2, 16, 64, 9), (24, 8, 32, 64, 64),
+                                            (5, 1, 48, 64, 17), (3, 3, 16, 128, 0)])
+def test_attention_on_the_tensor_cores(H, G, d, e, window):
+    assert F().attention_mix_tc_supported(H, G, d, e)
+    assert not F().attention_mix_tc_supported(24, 8, 128, 128) and not F().attention_mix_tc_supported(4, 2, 20, 64)
+    T = 330
+    g = torch.Generator().manual_seed(H + d)
+    q, k, v = (torch.randn(T, n, s, generator=g).to(torch.bfloat16).float() for n, s in ((H, d), (G, d), (G, e)))
+    talk = torch.eye(H) + 0.3 * torch.randn(H, H, generator=g)
+    want = pv.mixed_head_attention(q.double(), k.double(), v.double(), d ** -0.5, 6.0, talk.double(), window or T)
+    tol = 1.5e-2 * float(want.abs().max())
+    for cuts in ([T], [200, 17, 3, 100] + [1] * 10, [310] + [1] * 20):
+        got = run_attention_tc(q, k, v, talk, window, d ** -0.5, 6.0, cuts)
+        assert float((got.double() - want).abs().max()) <= tol, cuts[:2]
+    want = pv.mixed_head_attention(q.double(), k.double(), v.double(), d ** -0.5, None, None, window or T)
+    got = run_attention_tc(q, k, v, None, window, d ** -0.5, None, [T - 1, 1])
+    assert float((got.double() - want).abs().max()) <= 1.5e-2 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("window", [1, 15, 16, 17, 128, 129, 257])
+@pytest.mark.parametrize("decoded", [False, True])
+def test_the_edge_of_the_window_on_the_tensor_cores(window, decoded):
+    T, H, G, d, e = 300, 4, 2, 16, 64
+    g = torch.Generator().manual_seed(window)
+    v = torch.randn(T, G, e, generator=g).to(torch.bfloat16).float()
+    for dist, seen in ((window - 1, True), (window, False)):
+        q = torch.zeros(T, H, d)
+        k = (torch.randn(T, G, d, generator=g) * 0.01).to(torch.bfloat16).float()
+        q[-1, :, 0] = 40.0
+        k[T - 1 - dist, :, 0] = 1.0
+        got = run_attention_tc(q, k, v, None, window, 1.0, None, [T - 1, 1] if decoded else [T - 7, 7])[-1]
+        hit = torch.allclose(got, v[T - 1 - dist].repeat_interleave(2, 0), atol=2e-2)
+        assert hit == seen, (window, dist, decoded)
