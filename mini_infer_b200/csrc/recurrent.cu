@@ -86,12 +86,14 @@ conv_state_update_kernel(const float* __restrict__ x, int ldx, float* __restrict
 // The two recurrences.  Block = 128 threads = 16 value columns x 8 lanes; lane r of a column holds, of that
 // column of S, the rows 4 (r + 8 m) .. 4 (r + 8 m) + 3 for m = 0 .. RP/4 - 1 (RP rows in all), so that the
 // vectors a token brings are read from shared memory sixteen bytes at a time and a sum over rows is four
-// independent chains inside a thread, then three exchanges among the eight lanes.  Tokens are prepared 8 at
-// a time by the whole block; a chunk's results go out together.
+// independent chains inside a thread, then three exchanges among the eight lanes.  Tokens come 16 at a time:
+// while the block walks one chunk, the raw rows of the next are on their way into a second buffer
+// (cp.async), then the whole block turns them into what the recurrence reads (unit vectors, decays, step
+// sizes), in place; a chunk's results go out together.
 // ---------------------------------------------------------------------------
 constexpr int kScanLanes = 8;
 constexpr int kScanCols = 128 / kScanLanes;
-constexpr int kScanChunk = 8;
+constexpr int kScanChunk = 16;
 
 __device__ __forceinline__ float lanes_sum(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
@@ -100,32 +102,75 @@ __device__ __forceinline__ float lanes_sum(float v) {
     return v;
 }
 
+// asynchronous copy of one float from global to shared memory (any 4-byte alignment)
+__device__ __forceinline__ void copy_async_f32(float* smem_dst, const float* src) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src));
+}
+// sixteen bytes; both addresses 16-byte aligned
+__device__ __forceinline__ void copy_async_16(float* smem_dst, const float* src) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+// all groups but the most recent one have landed
+__device__ __forceinline__ void copy_async_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+
 // row of S that element (m, x) of lane r holds
 __device__ __forceinline__ int scan_row(int r, int m, int x) { return 4 * (r + kScanLanes * m) + x; }
 
-// qkv: [T, ld_qkv] float, q heads at column 0 (G x d), k heads at G*d, v heads at 2*G*d (H x dv), all after
-// the convolution; beta_raw: [T, ld_beta] at its own pointer (H columns); a_raw: [T, ld_a] (H x d columns,
-// before dt_bias and softplus).  out: [T, H*dv] float.
+// What the delta rule reads per (token, head), made ready by a kernel of its own (all tokens at once, instead
+// of once per slice of value columns inside the walk): prep[t][h] = [unit q * q_scale | unit k | decay | beta, 0, 0, 0],
+// the three vectors padded to DP rows with 0, 0 and 1.  qkv: [T, ld_qkv] float, q heads at column 0 (G x d),
+// k heads at G*d; beta_raw: [T, ld_beta] (H columns); a_raw: [T, ld_a] (H x d columns, before dt_bias and
+// softplus).
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __restrict__ beta_raw, int ld_beta,
+                     const float* __restrict__ a_raw, int ld_a, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, float* __restrict__ prep, int H, int G, int d, int DP,
+                     float q_scale) {
+    __shared__ float scratch[32];
+    wait_for_earlier_kernels();
+    const int64_t t = blockIdx.x;
+    const int h = blockIdx.y, hk = h / (H / G);
+    const float* qrow = qkv + t * ld_qkv + (int64_t)hk * d;
+    const float* krow = qkv + t * ld_qkv + (int64_t)(G + hk) * d;
+    const float* arow = a_raw + t * ld_a + (int64_t)h * d;
+    float qq = 0.f, kk = 0.f;
+    for (int i = threadIdx.x; i < d; i += 128) { const float a = qrow[i], c = krow[i]; qq += a * a; kk += c * c; }
+    qq = block_sum(qq, scratch);
+    kk = block_sum(kk, scratch);
+    const float qn = q_scale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
+    const float neg_a = -expf(a_log[h]);
+    float* row = prep + (t * H + h) * (3 * DP + 4);
+    for (int i = threadIdx.x; i < DP; i += 128) {
+        float qv = 0.f, kv = 0.f, gv = 1.f;
+        if (i < d) {
+            qv = qrow[i] * qn;
+            kv = krow[i] * kn;
+            gv = expf(neg_a * softplus_f(arow[i] + dt_bias[(int64_t)h * d + i]));
+        }
+        row[i] = qv; row[DP + i] = kv; row[2 * DP + i] = gv;
+    }
+    if (threadIdx.x < 4) row[3 * DP + threadIdx.x] = threadIdx.x == 0 ? sigmoid_f(beta_raw[t * ld_beta + h]) : 0.f;
+}
+
+// The walk.  prep as delta_prepare_kernel leaves it; v heads at column v_col0 of qkv (H x dv).  out: [T, H*dv].
 template <int RP>
 __global__ void __launch_bounds__(128)
-delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __restrict__ beta_raw, int ld_beta,
-                  const float* __restrict__ a_raw, int ld_a, const float* __restrict__ a_log,
-                  const float* __restrict__ dt_bias, float* __restrict__ state, int64_t state_stride,
-                  const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ out,
-                  int H, int G, int d, int dv, float q_scale) {
+delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, const float* __restrict__ prep,
+                  float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
+                  const int* __restrict__ state_slot, float* __restrict__ out, int H, int d, int dv) {
     extern __shared__ __align__(16) float sm[];
     constexpr int DP = RP * kScanLanes;                 // rows, padded
     constexpr int MV = RP / 4;
-    float* qs = sm;                                     // [chunk][DP] unit q times q_scale
-    float* ks = qs + kScanChunk * DP;                   // [chunk][DP] unit k
-    float* gs = ks + kScanChunk * DP;                   // [chunk][DP] decay
-    float* vs = gs + kScanChunk * DP;                   // [chunk][16] v of this slice
-    float* os = vs + kScanChunk * kScanCols;            // [chunk][16] results of the chunk
-    float* bs = os + kScanChunk * kScanCols;            // [chunk] beta
+    constexpr int ROW = 3 * DP + 4;                     // floats of one (token, head) of prep
+    // two buffers of: prep rows [chunk][ROW], v of this slice [chunk][16]
+    constexpr int kBuf = kScanChunk * (ROW + kScanCols);
+    float* os = sm + 2 * kBuf;                          // [chunk][16] results of the chunk
     wait_for_earlier_kernels();
     const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * kScanCols;
-    const int hk = h / (H / G);
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
     const int r = tid & (kScanLanes - 1), lc = tid / kScanLanes, col = col0 + lc;
     const bool col_ok = col < dv;
     const int q0 = q_start[b], n = q_start[b + 1] - q0;
@@ -138,41 +183,37 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __rest
             const int i = scan_row(r, m, x);
             s[4 * m + x] = (col_ok && i < d) ? S[(int64_t)i * dv + col] : 0.f;
         }
-    const float neg_a = -expf(a_log[h]);
-    for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+    const int64_t v_col = v_col0 + (int64_t)h * dv + col0;
+    const int n_cols = min(kScanCols, dv - col0);
+
+    auto fetch = [&](int c0, float* buf) {
         const int nc = min(kScanChunk, n - c0);
-        __syncthreads();                                // the chunk before has been consumed and written out
-        // a warp prepares tokens warp, warp + 4 of the chunk
-        for (int tt = warp; tt < nc; tt += 4) {
-            const int64_t t = q0 + c0 + tt;
-            const float* qrow = qkv + t * ld_qkv + (int64_t)hk * d;
-            const float* krow = qkv + t * ld_qkv + (int64_t)(G + hk) * d;
-            float qq = 0.f, kk = 0.f;
-            for (int i = lane; i < d; i += 32) { const float a = qrow[i], c = krow[i]; qq += a * a; kk += c * c; }
-            qq = warp_sum(qq);
-            kk = warp_sum(kk);
-            const float qn = q_scale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
-            const float* arow = a_raw + t * ld_a + (int64_t)h * d;
-            for (int i = lane; i < DP; i += 32) {
-                float qv = 0.f, kv = 0.f, gv = 1.f;
-                if (i < d) {
-                    qv = qrow[i] * qn;
-                    kv = krow[i] * kn;
-                    gv = expf(neg_a * softplus_f(arow[i] + dt_bias[(int64_t)h * d + i]));
-                }
-                qs[tt * DP + i] = qv; ks[tt * DP + i] = kv; gs[tt * DP + i] = gv;
-            }
-            if (lane < kScanCols) {
-                const int cc = col0 + lane;
-                vs[tt * kScanCols + lane] = cc < dv ? qkv[t * ld_qkv + (int64_t)2 * G * d + (int64_t)h * dv + cc] : 0.f;
-            }
-            if (lane == 0) bs[tt] = sigmoid_f(beta_raw[t * ld_beta + h]);
+        float* vs = buf + kScanChunk * ROW;
+        for (int idx = tid; idx < nc * (ROW / 4); idx += 128) {
+            const int tt = idx / (ROW / 4), c = idx - tt * (ROW / 4);
+            copy_async_16(buf + tt * ROW + 4 * c, prep + ((int64_t)(q0 + c0 + tt) * H + h) * ROW + 4 * c);
         }
-        __syncthreads();
+        for (int idx = tid; idx < nc * n_cols; idx += 128) {
+            const int tt = idx / n_cols, c = idx - tt * n_cols;
+            copy_async_f32(vs + tt * kScanCols + c, qkv + (int64_t)(q0 + c0 + tt) * ld_qkv + v_col + c);
+        }
+    };
+
+    fetch(0, sm);
+    copy_async_commit();
+    int which = 0;
+    for (int c0 = 0; c0 < n; c0 += kScanChunk, which ^= 1) {
+        const int nc = min(kScanChunk, n - c0);
+        const float* rows = sm + which * kBuf;
+        const float* vs = rows + kScanChunk * ROW;
+        if (c0 + kScanChunk < n) fetch(c0 + kScanChunk, sm + (which ^ 1) * kBuf);     // read last two syncs ago
+        copy_async_commit();
+        copy_async_wait_but_one();
+        __syncthreads();                                // this chunk's rows have landed for every thread
         for (int tt = 0; tt < nc; ++tt) {
-            const float4* kq = reinterpret_cast<const float4*>(ks + tt * DP);
-            const float4* gq = reinterpret_cast<const float4*>(gs + tt * DP);
-            const float4* qq = reinterpret_cast<const float4*>(qs + tt * DP);
+            const float4* qq = reinterpret_cast<const float4*>(rows + tt * ROW);
+            const float4* kq = qq + DP / 4;
+            const float4* gq = kq + DP / 4;
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
             for (int m = 0; m < MV; ++m) {
@@ -181,7 +222,7 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, const float* __rest
                 a0 += s[4 * m] * k4.x; a1 += s[4 * m + 1] * k4.y; a2 += s[4 * m + 2] * k4.z; a3 += s[4 * m + 3] * k4.w;
             }
             const float acc = lanes_sum((a0 + a1) + (a2 + a3));
-            const float u = bs[tt] * (vs[tt * kScanCols + lc] - acc);
+            const float u = rows[tt * ROW + 3 * DP] * (vs[tt * kScanCols + lc] - acc);
             float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
             for (int m = 0; m < MV; ++m) {
@@ -214,15 +255,13 @@ __global__ void __launch_bounds__(128)
 ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict__ dt_raw, int ld_dt,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                 float* __restrict__ state, int64_t state_stride, const int* __restrict__ q_start,
-                const int* __restrict__ state_slot, float* __restrict__ out, int H, int G, int N, int P) {
+                const int* __restrict__ state_slot, float* __restrict__ out, int H, int G, int N, int P, int vec) {
     extern __shared__ __align__(16) float sm[];
     constexpr int NP = RP * kScanLanes;
     constexpr int MV = RP / 4;
-    float* Bs = sm;                                     // [chunk][NP] dt * B
-    float* Cs = Bs + kScanChunk * NP;                   // [chunk][NP]
-    float* xs = Cs + kScanChunk * NP;                   // [chunk][16]
-    float* os = xs + kScanChunk * kScanCols;            // [chunk][16]
-    float* as = os + kScanChunk * kScanCols;            // [chunk] decay
+    // two buffers of: B, C [chunk][NP] each, x of this slice [chunk][16], step size input [chunk], decay [chunk]
+    constexpr int kBuf = kScanChunk * (2 * NP + kScanCols + 2);
+    float* os = sm + 2 * kBuf;                          // [chunk][16] results of the chunk
     wait_for_earlier_kernels();
     const int b = blockIdx.z, h = blockIdx.y, col0 = blockIdx.x * kScanCols;
     const int g = h / (H / G);
@@ -242,22 +281,59 @@ ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
     const float neg_a = -expf(a_log[h]);
     const float dskip = d_skip[h];
     const float bias = dt_bias[h];
-    for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+    const int n_cols = min(kScanCols, P - col0);
+
+    auto fetch = [&](int c0, float* buf) {
         const int nc = min(kScanChunk, n - c0);
+        float* Bs = buf;
+        float* Cs = Bs + kScanChunk * NP;
+        float* xs = Cs + kScanChunk * NP;
+        float* ds = xs + kScanChunk * kScanCols;
+        if (vec) {          // rows of B and C that start on 16-byte boundaries: four floats at a time
+            const int N4 = N / 4;
+            for (int idx = tid; idx < nc * N4; idx += 128) {
+                const int tt = idx / N4, i = 4 * (idx - tt * N4);
+                const float* brow = xbc + (int64_t)(q0 + c0 + tt) * ld_x + (int64_t)H * P + (int64_t)g * N;
+                copy_async_16(Bs + tt * NP + i, brow + i);
+                copy_async_16(Cs + tt * NP + i, brow + (int64_t)G * N + i);
+            }
+        } else {
+            for (int idx = tid; idx < nc * N; idx += 128) {
+                const int tt = idx / N, i = idx - tt * N;
+                const float* brow = xbc + (int64_t)(q0 + c0 + tt) * ld_x + (int64_t)H * P + (int64_t)g * N;
+                copy_async_f32(Bs + tt * NP + i, brow + i);
+                copy_async_f32(Cs + tt * NP + i, brow + (int64_t)G * N + i);
+            }
+        }
+        for (int idx = tid; idx < nc * n_cols; idx += 128) {
+            const int tt = idx / n_cols, c = idx - tt * n_cols;
+            copy_async_f32(xs + tt * kScanCols + c, xbc + (int64_t)(q0 + c0 + tt) * ld_x + (int64_t)h * P + col0 + c);
+        }
+        if (tid < nc) copy_async_f32(ds + tid, dt_raw + (int64_t)(q0 + c0 + tid) * ld_dt + h);
+    };
+
+    fetch(0, sm);
+    copy_async_commit();
+    int which = 0;
+    for (int c0 = 0; c0 < n; c0 += kScanChunk, which ^= 1) {
+        const int nc = min(kScanChunk, n - c0);
+        float* Bs = sm + which * kBuf;
+        float* Cs = Bs + kScanChunk * NP;
+        float* xs = Cs + kScanChunk * NP;
+        float* ds = xs + kScanChunk * kScanCols;
+        float* as = ds + kScanChunk;
+        if (c0 + kScanChunk < n) fetch(c0 + kScanChunk, sm + (which ^ 1) * kBuf);
+        copy_async_commit();
+        copy_async_wait_but_one();
         __syncthreads();
+        // step sizes and decays; B times the step size; zeros beyond the state's rows
         for (int tt = warp; tt < nc; tt += 4) {
-            const int64_t t = q0 + c0 + tt;
-            const float dt = softplus_f(dt_raw[t * ld_dt + h] + bias);
-            const float* brow = xbc + t * ld_x + (int64_t)H * P + (int64_t)g * N;
-            const float* crow = brow + (int64_t)G * N;
+            const float dt = softplus_f(ds[tt] + bias);
             for (int i = lane; i < NP; i += 32) {
-                Bs[tt * NP + i] = i < N ? dt * brow[i] : 0.f;
-                Cs[tt * NP + i] = i < N ? crow[i] : 0.f;
+                Bs[tt * NP + i] = i < N ? dt * Bs[tt * NP + i] : 0.f;
+                if (i >= N) Cs[tt * NP + i] = 0.f;
             }
-            if (lane < kScanCols) {
-                const int cc = col0 + lane;
-                xs[tt * kScanCols + lane] = cc < P ? xbc[t * ld_x + (int64_t)h * P + cc] : 0.f;
-            }
+            __syncwarp();
             if (lane == 0) as[tt] = expf(neg_a * dt);
         }
         __syncthreads();
@@ -361,22 +437,29 @@ int mi_causal_conv_silu(const float* x, int ldx, const void* w, const void* bias
         else { constexpr int RP = 32; __VA_ARGS__; }                                    \
     } while (0)
 
+// floats of one (token, head) of the scratch that mi_delta_scan needs: T * H * this many
+int mi_delta_scan_prep_row(int d) { return 3 * (d <= 64 ? 64 : (d <= 128 ? 128 : 256)) + 4; }
+
 int mi_delta_scan(const float* qkv, int ld_qkv, const float* beta_raw, int ld_beta, const float* a_raw, int ld_a,
                   const float* a_log, const float* dt_bias, float* state, int64_t state_stride, const int* q_start,
-                  const int* state_slot, float* out, int B, int H, int G, int d, int dv, float q_scale,
-                  cudaStream_t stream) {
-    if (B <= 0) return kOk;
+                  const int* state_slot, float* out, float* prep, int T, int B, int H, int G, int d, int dv,
+                  float q_scale, cudaStream_t stream) {
+    if (B <= 0 || T <= 0) return kOk;
     if (d < 1 || d > 256 || dv < 1) { set_last_error("delta rule: key size %d outside [1, 256] or value size %d", d, dv); return kBadShape; }
     if (G < 1 || H % G) { set_last_error("delta rule: %d heads are not a multiple of %d key heads", H, G); return kBadShape; }
     if (B > 65535 || H > 65535) { set_last_error("delta rule: batch %d or heads %d exceed the grid limit", B, H); return kBadShape; }
+    if (!prep || (reinterpret_cast<uintptr_t>(prep) & 15)) { set_last_error("delta rule: the scratch is missing or not 16-byte aligned"); return kBadShape; }
+    const int DP = d <= 64 ? 64 : (d <= 128 ? 128 : 256);
+    launch_dependent(delta_prepare_kernel, dim3(T, H), dim3(128), 0, stream, qkv, ld_qkv, beta_raw, ld_beta, a_raw, ld_a,
+                     a_log, dt_bias, prep, H, G, d, DP, q_scale);
     const dim3 grid((dv + kScanCols - 1) / kScanCols, H, B);
     MI_SCAN_DISPATCH(d, {
-        const size_t smem = sizeof(float) * (kScanChunk * (3 * RP * kScanLanes + 2 * kScanCols + 1));
-        launch_dependent(delta_scan_kernel<RP>, grid, dim3(128), smem, stream, qkv, ld_qkv,
-                         beta_raw, ld_beta, a_raw, ld_a, a_log, dt_bias, state, state_stride, q_start, state_slot,
-                         out, H, G, d, dv, q_scale);
+        const size_t smem = sizeof(float) * (2 * kScanChunk * (3 * RP * kScanLanes + 4 + kScanCols) + kScanChunk * kScanCols);
+        cudaFuncSetAttribute(delta_scan_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_dependent(delta_scan_kernel<RP>, grid, dim3(128), smem, stream, qkv, ld_qkv, (int64_t)2 * G * d,
+                         (const float*)prep, state, state_stride, q_start, state_slot, out, H, d, dv);
     });
-    return finish_launch("delta_scan");
+    return finish_launch("delta_scan", 2);
 }
 
 int mi_ssd_scan(const float* xbc, int ld_x, const float* dt_raw, int ld_dt, const float* dt_bias, const float* a_log,
@@ -387,10 +470,12 @@ int mi_ssd_scan(const float* xbc, int ld_x, const float* dt_raw, int ld_dt, cons
     if (G < 1 || H % G) { set_last_error("state-space scan: %d heads are not a multiple of %d groups", H, G); return kBadShape; }
     if (B > 65535 || H > 65535) { set_last_error("state-space scan: batch %d or heads %d exceed the grid limit", B, H); return kBadShape; }
     const dim3 grid((P + kScanCols - 1) / kScanCols, H, B);
+    const int vec = (N % 4 == 0 && ld_x % 4 == 0 && (H * P) % 4 == 0 && (reinterpret_cast<uintptr_t>(xbc) & 15) == 0) ? 1 : 0;
     MI_SCAN_DISPATCH(N, {
-        const size_t smem = sizeof(float) * (kScanChunk * (2 * RP * kScanLanes + 2 * kScanCols + 1));
+        const size_t smem = sizeof(float) * (2 * kScanChunk * (2 * RP * kScanLanes + kScanCols + 2) + kScanChunk * kScanCols);
+        cudaFuncSetAttribute(ssd_scan_kernel<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         launch_dependent(ssd_scan_kernel<RP>, grid, dim3(128), smem, stream, xbc, ld_x, dt_raw,
-                         ld_dt, dt_bias, a_log, d_skip, state, state_stride, q_start, state_slot, out, H, G, N, P);
+                         ld_dt, dt_bias, a_log, d_skip, state, state_stride, q_start, state_slot, out, H, G, N, P, vec);
     });
     return finish_launch("ssd_scan");
 }

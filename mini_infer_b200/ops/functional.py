@@ -1020,10 +1020,13 @@ def delta_scan(qkv: torch.Tensor, beta_raw: torch.Tensor, beta_col: int, a_raw: 
     if DEBUG_BOUNDS:
         _dbg_range(state_slot, 0, state.shape[0], "delta_scan state_slot")
     out = torch.empty(T, heads * dv, dtype=F32, device=qkv.device)
+    # unit vectors, decays and write strengths of all tokens, made ready by a kernel before the walk
+    prep = torch.empty(T * heads * library().mi_delta_scan_prep_row(d), dtype=F32, device=qkv.device)
     check(library().mi_delta_scan(_ptr(qkv), qkv.shape[1], beta_raw.data_ptr() + 4 * beta_col, beta_raw.shape[1],
                                   a_raw.data_ptr() + 4 * a_col, a_raw.shape[1], _ptr(a_log), _ptr(dt_bias),
                                   state.data_ptr() + 4 * state_offset, state.shape[1], _ptr(q_start), _ptr(state_slot),
-                                  _ptr(out), B, heads, key_heads, d, dv, float(q_scale), _stream()), "delta_scan")
+                                  _ptr(out), _ptr(prep), T, B, heads, key_heads, d, dv, float(q_scale), _stream()),
+          "delta_scan")
     return out
 
 

@@ -48,7 +48,7 @@ _SIGNATURES = {
     "mi_dense_f32": [P, P, P, I, I, I, P],
     "mi_l2_prefetch": [P, ctypes.c_ulonglong, P],
     "mi_causal_conv_silu": [P, I, P, P, I, P, L, P, P, P, P, I, I, I, I, I, P],
-    "mi_delta_scan": [P, I, P, I, P, I, P, P, P, L, P, P, P, I, I, I, I, I, F, P],
+    "mi_delta_scan": [P, I, P, I, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, P],
     "mi_ssd_scan": [P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, P],
     "mi_gated_group_rmsnorm": [P, P, I, P, I, I, P, I, I, I, I, I, F, P],
     "mi_rope_store": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
@@ -106,6 +106,8 @@ def library() -> ctypes.CDLL:
     lib.mi_qkv_skinny_supported.restype = c_int
     lib.mi_dense_skinny_max_rows.argtypes = []
     lib.mi_dense_skinny_max_rows.restype = c_int
+    lib.mi_delta_scan_prep_row.argtypes = [I]
+    lib.mi_delta_scan_prep_row.restype = c_int
     lib.mi_attn_mix_tc_supported.argtypes = [I, I, I, I]
     lib.mi_attn_mix_tc_supported.restype = c_int
     lib.mi_attn_mix_tc_splits.argtypes = [I]
