@@ -12,9 +12,10 @@
 // and unnormalised output; a merge kernel finishes), since one block per request cannot pull a window of
 // keys from memory fast enough.
 //
-// Built for value sizes 64 and 128, key sizes that are multiples of 16, up to 16 heads of value size 128 or
-// 32 of 64 (the accumulators of all heads of 16 queries must fit the registers of one block); other shapes
-// and the float path take the kernel of attention_mix.cu.
+// Built for value sizes 64 and 128 and key sizes that are multiples of 16.  The accumulators of 16 heads of
+// value size 128 (32 of 64) fill one block's registers; with more heads several blocks share a query tile,
+// each forming all heads' scores and finishing its own group of heads.  Shapes whose tiles do not fit shared
+// memory, other sizes and the float path take the kernel of attention_mix.cu.
 
 #include "common.cuh"
 
@@ -30,6 +31,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// tanh and exp of the bfloat16 path: the hardware's exponential (a few units in the last place), where the
+// library functions cost thirty to forty instructions apiece, a third of a key tile's work
+__device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
+
 constexpr int kTcQ = 16;          // queries per block
 constexpr int kTcWarps = 8;
 constexpr int kTcSplitKeys = 128; // keys per block of a split step
@@ -41,12 +46,16 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ block_table, const int* __restrict__ q_start,
                    const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int H, int G, int dk, int page_size, int max_pages, int window,
-                   float scale, float cap, int splits) {
+                   float scale, float cap, int splits, int hgroups) {
     constexpr int DV = NT * 8;
     constexpr int SP = KT + 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     wait_for_earlier_kernels();
-    const int b = blockIdx.y, qt = blockIdx.x, split = blockIdx.z;
+    // with more heads than one block's registers hold accumulators for, `hgroups` blocks share a query tile:
+    // each forms all heads' scores (the mix needs them) and finishes the heads [h_lo, h_hi) only
+    const int b = blockIdx.y, qt = blockIdx.x / hgroups, hg = blockIdx.x % hgroups, split = blockIdx.z;
+    const int HG = (H + hgroups - 1) / hgroups;
+    const int h_lo = hg * HG, h_hi = min(H, h_lo + HG);
     const int q0 = q_start[b], q_len = q_start[b + 1] - q0;
     if (qt * kTcQ >= q_len) return;
     const int kvl = kv_len[b];
@@ -56,8 +65,8 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int dkp = dk + 8, dvp = DV + 8;
     const int kv_stride = dkp > dvp ? dkp : dvp;
     float* S1 = reinterpret_cast<float*>(smem_raw);                       // [H][16][SP]
-    float* S2 = S1 + H * kTcQ * SP;                                       // [H][16][SP]
-    float* Mx = S2 + H * kTcQ * SP;                                       // [H][H]
+    float* S2 = S1 + H * kTcQ * SP;                                       // [HG][16][SP], heads of this block
+    float* Mx = S2 + HG * kTcQ * SP;                                      // [H][H]
     int* slot_of = reinterpret_cast<int*>(Mx + ((H * H + 3) & ~3));       // [KT]
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(slot_of + KT + ((4 - KT % 4) % 4));   // [H][16][dkp]
     __nv_bfloat16* KV = Qs + (size_t)H * kTcQ * dkp;                      // [G][KT][kv_stride]
@@ -74,7 +83,8 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         if (i < nq) v = *reinterpret_cast<const uint4*>(q + ((size_t)(q0 + qt * kTcQ + i) * H + h) * dk + c8 * 8);
         *reinterpret_cast<uint4*>(Qs + ((size_t)h * kTcQ + i) * dkp + c8 * 8) = v;
     }
-    if (mix) for (int idx = tid; idx < H * H; idx += 256) Mx[idx] = mix[idx];
+    // transposed: Mx[g * H + h] = mix[h][g], so that four heads' weights of one g are one 16-byte read
+    if (mix) for (int idx = tid; idx < H * H; idx += 256) Mx[(idx % H) * H + idx / H] = mix[idx];
 
     float acc[HPW][NT][4];
     float m_run[HPW][2], l_run[HPW][2];
@@ -97,6 +107,7 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         k_end = min(k_end, k_begin + kTcSplitKeys);
     }
     const int* table = block_table + (size_t)b * max_pages;
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
     for (int kt = k_begin; kt < k_end; kt += KT) {
         __syncthreads();
@@ -121,11 +132,9 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             *reinterpret_cast<uint4*>(KV + ((size_t)g * KT + j) * kv_stride + c8 * 8) = v;
         }
         __syncthreads();
-        // ---- scores ----
-#pragma unroll
-        for (int hh = 0; hh < HPW; ++hh) {
-            const int h = warp + kTcWarps * hh;
-            if (h < H) {
+        // ---- scores of all heads ----
+        for (int h = warp; h < H; h += kTcWarps) {
+            {
                 const int g = h / rep;
                 float c[KT / 8][4];
 #pragma unroll
@@ -153,7 +162,7 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
                     for (int x = 0; x < 4; ++x) {
                         float s = c[nt][x] * scale;
-                        if (cap > 0.f) s = cap * tanhf(s / cap);
+                        if (cap > 0.f) s = cap * fast_tanh(s * inv_cap);
                         sb[(r0 + (x >> 1) * 8) * SP + nt * 8 + c2 + (x & 1)] = s;
                     }
             }
@@ -175,25 +184,39 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             const int i = e / KT, j = e - i * KT;
             const int kj = kt + j, pos = p_lo + i;
             const bool vis = i < nq && kj <= pos && (window == 0 || kj > pos - window) && slot_of[j] >= 0;
-            for (int h = 0; h < H; ++h) {
-                float s;
-                if (mix) {
-                    s = 0.f;
-                    for (int g = 0; g < H; ++g) s += Mx[h * H + g] * S1[(g * kTcQ + i) * SP + j];
-                } else {
-                    s = S1[(h * kTcQ + i) * SP + j];
+            if (!vis) {
+                for (int h = h_lo; h < h_hi; ++h) S2[((h - h_lo) * kTcQ + i) * SP + j] = -INFINITY;
+            } else if (!mix) {
+                for (int h = h_lo; h < h_hi; ++h) S2[((h - h_lo) * kTcQ + i) * SP + j] = S1[(h * kTcQ + i) * SP + j];
+            } else if (((H | HG) & 3) == 0) {
+                for (int h = h_lo; h < h_hi; h += 4) {
+                    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+                    for (int g = 0; g < H; ++g) {
+                        const float v = S1[(g * kTcQ + i) * SP + j];
+                        const float4 w = *reinterpret_cast<const float4*>(Mx + g * H + h);
+                        s0 += w.x * v; s1 += w.y * v; s2 += w.z * v; s3 += w.w * v;
+                    }
+                    S2[((h - h_lo) * kTcQ + i) * SP + j] = s0;
+                    S2[((h - h_lo + 1) * kTcQ + i) * SP + j] = s1;
+                    S2[((h - h_lo + 2) * kTcQ + i) * SP + j] = s2;
+                    S2[((h - h_lo + 3) * kTcQ + i) * SP + j] = s3;
                 }
-                S2[(h * kTcQ + i) * SP + j] = vis ? s : -INFINITY;
+            } else {
+                for (int h = h_lo; h < h_hi; ++h) {
+                    float s = 0.f;
+                    for (int g = 0; g < H; ++g) s += Mx[g * H + h] * S1[(g * kTcQ + i) * SP + j];
+                    S2[((h - h_lo) * kTcQ + i) * SP + j] = s;
+                }
             }
         }
         __syncthreads();
-        // ---- softmax and P.V ----
+        // ---- softmax and P.V of this block's heads ----
 #pragma unroll
         for (int hh = 0; hh < HPW; ++hh) {
-            const int h = warp + kTcWarps * hh;
-            if (h < H) {
+            const int h = h_lo + warp + kTcWarps * hh;
+            if (h < h_hi) {
                 const int g = h / rep;
-                const float* sb = S2 + (size_t)h * kTcQ * SP;
+                const float* sb = S2 + (size_t)(h - h_lo) * kTcQ * SP;
                 float p[KT / 8][4];
                 float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -210,15 +233,15 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                 mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
                 mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
                 const float mn0 = fmaxf(m_run[hh][0], mx0), mn1 = fmaxf(m_run[hh][1], mx1);
-                const float al0 = mn0 == -INFINITY ? 1.f : expf(m_run[hh][0] - mn0);
-                const float al1 = mn1 == -INFINITY ? 1.f : expf(m_run[hh][1] - mn1);
+                const float al0 = mn0 == -INFINITY ? 1.f : __expf(m_run[hh][0] - mn0);
+                const float al1 = mn1 == -INFINITY ? 1.f : __expf(m_run[hh][1] - mn1);
                 float s0 = 0.f, s1 = 0.f;
 #pragma unroll
                 for (int nt = 0; nt < KT / 8; ++nt) {
-                    p[nt][0] = mn0 == -INFINITY ? 0.f : expf(p[nt][0] - mn0);
-                    p[nt][1] = mn0 == -INFINITY ? 0.f : expf(p[nt][1] - mn0);
-                    p[nt][2] = mn1 == -INFINITY ? 0.f : expf(p[nt][2] - mn1);
-                    p[nt][3] = mn1 == -INFINITY ? 0.f : expf(p[nt][3] - mn1);
+                    p[nt][0] = mn0 == -INFINITY ? 0.f : __expf(p[nt][0] - mn0);
+                    p[nt][1] = mn0 == -INFINITY ? 0.f : __expf(p[nt][1] - mn0);
+                    p[nt][2] = mn1 == -INFINITY ? 0.f : __expf(p[nt][2] - mn1);
+                    p[nt][3] = mn1 == -INFINITY ? 0.f : __expf(p[nt][3] - mn1);
                     s0 += p[nt][0] + p[nt][1];
                     s1 += p[nt][2] + p[nt][3];
                 }
@@ -252,8 +275,8 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     // ---- results ----
 #pragma unroll
     for (int hh = 0; hh < HPW; ++hh) {
-        const int h = warp + kTcWarps * hh;
-        if (h < H) {
+        const int h = h_lo + warp + kTcWarps * hh;
+        if (h < h_hi) {
             float l0 = l_run[hh][0], l1 = l_run[hh][1];
             l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
             l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
@@ -312,21 +335,28 @@ attn_mix_merge_kernel(const float* __restrict__ part_o, const float* __restrict_
     }
 }
 
-static size_t tc_smem(int H, int G, int dk, int dv, int kt) {
+static size_t tc_smem(int H, int HG, int G, int dk, int dv, int kt) {
     const int dkp = dk + 8, dvp = dv + 8;
     const int kvs = dkp > dvp ? dkp : dvp;
-    return (size_t)2 * H * kTcQ * (kt + 1) * 4 + (size_t)((H * H + 3) & ~3) * 4 + (size_t)(kt + 4) * 4 + (size_t)H * kTcQ * dkp * 2 +
-           (size_t)G * kt * kvs * 2 + 16;
+    return (size_t)(H + HG) * kTcQ * (kt + 1) * 4 + (size_t)((H * H + 3) & ~3) * 4 + (size_t)(kt + 4) * 4 +
+           (size_t)H * kTcQ * dkp * 2 + (size_t)G * kt * kvs * 2 + 16;
 }
 
-// keys per tile for a model's sizes (0: the shape is not taken)
-static int tc_plan(int H, int G, int dk, int dv) {
-    if (H < 1 || G < 1 || H % G || dk % 16 || dk < 16 || dk > 256 || (dv != 64 && dv != 128)) return 0;
-    const int hpw = (H + kTcWarps - 1) / kTcWarps;
-    if (hpw * (dv / 8) > 32) return 0;
-    if (tc_smem(H, G, dk, dv, 32) <= 220 * 1024) return 32;
-    if (tc_smem(H, G, dk, dv, 16) <= 220 * 1024) return 16;
-    return 0;
+struct TcPlan { int kt, hgroups, hpw; };
+
+// keys per tile, blocks per query tile and heads per warp for a model's sizes (kt 0: the shape is not taken)
+static TcPlan tc_plan(int H, int G, int dk, int dv) {
+    TcPlan p = {0, 1, 1};
+    if (H < 1 || G < 1 || H % G || dk % 16 || dk < 16 || dk > 256 || (dv != 64 && dv != 128)) return p;
+    const int max_hpw = 32 / (dv / 8);                  // accumulators of a warp: hpw * dv / 8 * 4 registers a lane
+    int hgroups = 1;
+    while (((H + hgroups - 1) / hgroups + kTcWarps - 1) / kTcWarps > max_hpw) ++hgroups;
+    const int HG = (H + hgroups - 1) / hgroups;
+    p.hgroups = hgroups;
+    p.hpw = (HG + kTcWarps - 1) / kTcWarps;
+    if (tc_smem(H, HG, G, dk, dv, 32) <= 220 * 1024) p.kt = 32;
+    else if (tc_smem(H, HG, G, dk, dv, 16) <= 220 * 1024) p.kt = 16;
+    return p;
 }
 
 }  // namespace mi
@@ -335,7 +365,7 @@ using namespace mi;
 
 extern "C" {
 
-int mi_attn_mix_tc_supported(int H, int G, int dk, int dv) { return tc_plan(H, G, dk, dv) > 0; }
+int mi_attn_mix_tc_supported(int H, int G, int dk, int dv) { return tc_plan(H, G, dk, dv).kt > 0; }
 
 // splits a step of single tokens is cut into, given the longest span of keys a query can see
 int mi_attn_mix_tc_splits(int span) { return (span + kTcSplitKeys - 1) / kTcSplitKeys + 1; }
@@ -345,7 +375,8 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
                    int max_q_len, int H, int G, int dk, int dv, int page_size, int max_pages, int window,
                    float scale, float cap, int splits, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return kOk;
-    const int kt = tc_plan(H, G, dk, dv);
+    const TcPlan plan = tc_plan(H, G, dk, dv);
+    const int kt = plan.kt;
     if (!kt) {
         set_last_error("mixed-head attention (tensor cores): heads %d/%d, key size %d, value size %d are not taken", H, G, dk, dv);
         return kBadShape;
@@ -354,16 +385,16 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
         set_last_error("mixed-head attention (tensor cores): %d splits with portions of %d tokens, batch %d", splits, max_q_len, B);
         return kBadShape;
     }
-    const int hpw = (H + kTcWarps - 1) / kTcWarps;
-    const size_t smem = tc_smem(H, G, dk, dv, kt);
-    const dim3 grid((max_q_len + kTcQ - 1) / kTcQ, B, splits);
+    const int hpw = plan.hpw, hgroups = plan.hgroups;
+    const size_t smem = tc_smem(H, (H + hgroups - 1) / hgroups, G, dk, dv, kt);
+    const dim3 grid(((max_q_len + kTcQ - 1) / kTcQ) * hgroups, B, splits);
 #define MI_TC_LAUNCH(HPW, NT, KT)                                                                               \
     do {                                                                                                        \
         cudaFuncSetAttribute(attn_mix_tc_kernel<HPW, NT, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         launch_dependent(attn_mix_tc_kernel<HPW, NT, KT>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)q, \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, mix, block_table, q_start, \
                          kv_len, (__nv_bfloat16*)out, part_o, part_ml, H, G, dk, page_size, max_pages, window,  \
-                         scale, cap, splits);                                                                   \
+                         scale, cap, splits, hgroups);                                                          \
     } while (0)
 #define MI_TC_KT(HPW, NT) do { if (kt == 32) MI_TC_LAUNCH(HPW, NT, 32); else MI_TC_LAUNCH(HPW, NT, 16); } while (0)
     if (dv == 128) {

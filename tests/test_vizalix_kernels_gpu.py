@@ -386,10 +386,12 @@ def run_attention_tc(q, k, v, talk, window, scale, cap, cuts, page_size=8):
 
 
 @pytest.mark.parametrize("H,G,d,e,window", [(16, 4, 64, 128, 40), (8, 4, 128, 128, 300), (4, 2, 16, 64, 9), (24, 8, 32, 64, 64),
-                                            (5, 1, 48, 64, 17), (3, 3, 16, 128, 0)])
+                                            (5, 1, 48, 64, 17), (3, 3, 16, 128, 0),
+                                            # more heads than one block finishes: two and three blocks share a query tile
+                                            (24, 8, 128, 128, 150), (40, 8, 32, 64, 33), (18, 3, 16, 128, 70)])
 def test_attention_on_the_tensor_cores(H, G, d, e, window):
     assert F().attention_mix_tc_supported(H, G, d, e)
-    assert not F().attention_mix_tc_supported(24, 8, 128, 128) and not F().attention_mix_tc_supported(4, 2, 20, 64)
+    assert not F().attention_mix_tc_supported(4, 2, 20, 64) and not F().attention_mix_tc_supported(4, 2, 32, 96)
     T = 330
     g = torch.Generator().manual_seed(H + d)
     q, k, v = (torch.randn(T, n, s, generator=g).to(torch.bfloat16).float() for n, s in ((H, d), (G, d), (G, e)))
