@@ -210,28 +210,45 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, con
         copy_async_commit();
         copy_async_wait_but_one();
         __syncthreads();                                // this chunk's rows have landed for every thread
-        for (int tt = 0; tt < nc; ++tt) {
-            const float4* qq = reinterpret_cast<const float4*>(rows + tt * ROW);
-            const float4* kq = qq + DP / 4;
-            const float4* gq = kq + DP / 4;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        // Four tokens at a time: the read-outs' sums over the lanes do not feed the recurrence, so the four of
+        // them are exchanged together after the four steps instead of stalling each step.
+        for (int t4 = 0; t4 < nc; t4 += 4) {
+            float o_part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int m = 0; m < MV; ++m) {
-                const float4 g4 = gq[r + kScanLanes * m], k4 = kq[r + kScanLanes * m];
-                s[4 * m] *= g4.x; s[4 * m + 1] *= g4.y; s[4 * m + 2] *= g4.z; s[4 * m + 3] *= g4.w;
-                a0 += s[4 * m] * k4.x; a1 += s[4 * m + 1] * k4.y; a2 += s[4 * m + 2] * k4.z; a3 += s[4 * m + 3] * k4.w;
-            }
-            const float acc = lanes_sum((a0 + a1) + (a2 + a3));
-            const float u = rows[tt * ROW + 3 * DP] * (vs[tt * kScanCols + lc] - acc);
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+            for (int u4 = 0; u4 < 4; ++u4) {
+                const int tt = t4 + u4;
+                if (tt < nc) {
+                    const float4* qq = reinterpret_cast<const float4*>(rows + tt * ROW);
+                    const float4* kq = qq + DP / 4;
+                    const float4* gq = kq + DP / 4;
+                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int m = 0; m < MV; ++m) {
-                const float4 k4 = kq[r + kScanLanes * m], q4 = qq[r + kScanLanes * m];
-                s[4 * m] += k4.x * u; s[4 * m + 1] += k4.y * u; s[4 * m + 2] += k4.z * u; s[4 * m + 3] += k4.w * u;
-                o0 += s[4 * m] * q4.x; o1 += s[4 * m + 1] * q4.y; o2 += s[4 * m + 2] * q4.z; o3 += s[4 * m + 3] * q4.w;
+                    for (int m = 0; m < MV; ++m) {
+                        const float4 g4 = gq[r + kScanLanes * m], k4 = kq[r + kScanLanes * m];
+                        s[4 * m] *= g4.x; s[4 * m + 1] *= g4.y; s[4 * m + 2] *= g4.z; s[4 * m + 3] *= g4.w;
+                        a0 += s[4 * m] * k4.x; a1 += s[4 * m + 1] * k4.y; a2 += s[4 * m + 2] * k4.z; a3 += s[4 * m + 3] * k4.w;
+                    }
+                    const float acc = lanes_sum((a0 + a1) + (a2 + a3));
+                    const float u = rows[tt * ROW + 3 * DP] * (vs[tt * kScanCols + lc] - acc);
+                    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+                    for (int m = 0; m < MV; ++m) {
+                        const float4 k4 = kq[r + kScanLanes * m], q4 = qq[r + kScanLanes * m];
+                        s[4 * m] += k4.x * u; s[4 * m + 1] += k4.y * u; s[4 * m + 2] += k4.z * u; s[4 * m + 3] += k4.w * u;
+                        o0 += s[4 * m] * q4.x; o1 += s[4 * m + 1] * q4.y; o2 += s[4 * m + 2] * q4.z; o3 += s[4 * m + 3] * q4.w;
+                    }
+                    o_part[u4] = (o0 + o1) + (o2 + o3);
+                }
             }
-            const float o = lanes_sum((o0 + o1) + (o2 + o3));
-            if (r == 0) os[tt * kScanCols + lc] = o;
+#pragma unroll
+            for (int sh = 1; sh < kScanLanes; sh <<= 1)
+#pragma unroll
+                for (int u4 = 0; u4 < 4; ++u4) o_part[u4] += __shfl_xor_sync(0xffffffffu, o_part[u4], sh);
+            if (r == 0) {
+#pragma unroll
+                for (int u4 = 0; u4 < 4; ++u4)
+                    if (t4 + u4 < nc) os[(t4 + u4) * kScanCols + lc] = o_part[u4];
+            }
         }
         __syncthreads();
         for (int idx = tid; idx < nc * kScanCols; idx += 128) {
@@ -259,7 +276,7 @@ ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
     extern __shared__ __align__(16) float sm[];
     constexpr int NP = RP * kScanLanes;
     constexpr int MV = RP / 4;
-    // two buffers of: B, C [chunk][NP] each, x of this slice [chunk][16], step size input [chunk], decay [chunk]
+    // two buffers of: B, C [chunk][NP] each, x of this slice [chunk][16], step size [chunk], decay [chunk]
     constexpr int kBuf = kScanChunk * (2 * NP + kScanCols + 2);
     float* os = sm + 2 * kBuf;                          // [chunk][16] results of the chunk
     wait_for_earlier_kernels();
@@ -282,6 +299,12 @@ ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
     const float dskip = d_skip[h];
     const float bias = dt_bias[h];
     const int n_cols = min(kScanCols, P - col0);
+    // rows beyond the state's size are never copied to: zero them once in both buffers
+    if (N < NP)
+        for (int idx = tid; idx < 2 * 2 * kScanChunk * (NP - N); idx += 128) {
+            const int i = N + idx % (NP - N), row = idx / (NP - N);      // row: buffer, B or C, token
+            sm[(row / (2 * kScanChunk)) * kBuf + (row % (2 * kScanChunk)) * NP + i] = 0.f;
+        }
 
     auto fetch = [&](int c0, float* buf) {
         const int nc = min(kScanChunk, n - c0);
@@ -326,31 +349,44 @@ ssd_scan_kernel(const float* __restrict__ xbc, int ld_x, const float* __restrict
         copy_async_commit();
         copy_async_wait_but_one();
         __syncthreads();
-        // step sizes and decays; B times the step size; zeros beyond the state's rows
-        for (int tt = warp; tt < nc; tt += 4) {
-            const float dt = softplus_f(ds[tt] + bias);
-            for (int i = lane; i < NP; i += 32) {
-                Bs[tt * NP + i] = i < N ? dt * Bs[tt * NP + i] : 0.f;
-                if (i >= N) Cs[tt * NP + i] = 0.f;
-            }
-            __syncwarp();
-            if (lane == 0) as[tt] = expf(neg_a * dt);
+        // step sizes and decays, a thread per token (the step size is folded into x in the walk)
+        if (tid < nc) {
+            const float dt = softplus_f(ds[tid] + bias);
+            ds[tid] = dt;
+            as[tid] = expf(neg_a * dt);
         }
         __syncthreads();
-        for (int tt = 0; tt < nc; ++tt) {
-            const float4* Bq = reinterpret_cast<const float4*>(Bs + tt * NP);
-            const float4* Cq = reinterpret_cast<const float4*>(Cs + tt * NP);
-            const float a = as[tt], xv = xs[tt * kScanCols + lc];
-            float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+        // Four tokens at a time: a token's read-out does not feed the recurrence, so the sums over the lanes of
+        // four read-outs are exchanged together after the four steps.
+        for (int t4 = 0; t4 < nc; t4 += 4) {
+            float y_part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int m = 0; m < MV; ++m) {
-                const float4 b4 = Bq[r + kScanLanes * m], c4 = Cq[r + kScanLanes * m];
-                s[4 * m] = a * s[4 * m] + b4.x * xv; s[4 * m + 1] = a * s[4 * m + 1] + b4.y * xv;
-                s[4 * m + 2] = a * s[4 * m + 2] + b4.z * xv; s[4 * m + 3] = a * s[4 * m + 3] + b4.w * xv;
-                y0 += s[4 * m] * c4.x; y1 += s[4 * m + 1] * c4.y; y2 += s[4 * m + 2] * c4.z; y3 += s[4 * m + 3] * c4.w;
+            for (int u4 = 0; u4 < 4; ++u4) {
+                const int tt = t4 + u4;
+                if (tt < nc) {
+                    const float4* Bq = reinterpret_cast<const float4*>(Bs + tt * NP);
+                    const float4* Cq = reinterpret_cast<const float4*>(Cs + tt * NP);
+                    const float a = as[tt], xv = ds[tt] * xs[tt * kScanCols + lc];     // decay; dt * x
+                    float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll
+                    for (int m = 0; m < MV; ++m) {
+                        const float4 b4 = Bq[r + kScanLanes * m], c4 = Cq[r + kScanLanes * m];
+                        s[4 * m] = a * s[4 * m] + b4.x * xv; s[4 * m + 1] = a * s[4 * m + 1] + b4.y * xv;
+                        s[4 * m + 2] = a * s[4 * m + 2] + b4.z * xv; s[4 * m + 3] = a * s[4 * m + 3] + b4.w * xv;
+                        y0 += s[4 * m] * c4.x; y1 += s[4 * m + 1] * c4.y; y2 += s[4 * m + 2] * c4.z; y3 += s[4 * m + 3] * c4.w;
+                    }
+                    y_part[u4] = (y0 + y1) + (y2 + y3);
+                }
             }
-            const float y = lanes_sum((y0 + y1) + (y2 + y3));
-            if (r == 0) os[tt * kScanCols + lc] = y + dskip * xv;
+#pragma unroll
+            for (int sh = 1; sh < kScanLanes; sh <<= 1)
+#pragma unroll
+                for (int u4 = 0; u4 < 4; ++u4) y_part[u4] += __shfl_xor_sync(0xffffffffu, y_part[u4], sh);
+            if (r == 0) {
+#pragma unroll
+                for (int u4 = 0; u4 < 4; ++u4)
+                    if (t4 + u4 < nc) os[(t4 + u4) * kScanCols + lc] = y_part[u4] + dskip * xs[(t4 + u4) * kScanCols + lc];
+            }
         }
         __syncthreads();
         for (int idx = tid; idx < nc * kScanCols; idx += 128) {
