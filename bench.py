@@ -538,11 +538,29 @@ def _vizalix_kernel_work(cfg, T, B, ctx, decode):
             else:
                 pairs = sum(min(t + 1, win) for t in range(T))
                 by = T * (H * (d + e) + G * (d + e)) * 2
-            add("attn_mix_kernel", n * by, n * pairs * H * (2.0 * d + 2.0 * e + 2.0 * H))
+            for name in ("attn_mix_kernel", "attn_mix_tc_kernel"):       # whichever form the sizes take
+                add(name, n * by, n * pairs * H * (2.0 * d + 2.0 * e + 2.0 * H))
             add("rope_store_kernel", n * rows * (H * d + G * (d + e)) * 6, 0)
         add("add2_rmsnorm_scalar_kernel", n * rows * W * (4 * 4 + 2 * 2), 0)
         add("geglu_tanh_kernel", n * rows * L["mlp"]["ff"] * 6, 0)
     return out
+
+
+def _twin_kernel_work(size, window, T, B, ctx, decode, layers):
+    """The same for the like kernels of the dense twin: attention, the two norms, the gated activation."""
+    W, H, G, d, ff = VIZALIX_SIZES[size]
+    rows = B if decode else T
+    if decode:
+        keys = min(ctx, window)
+        pairs, by = B * keys, B * keys * G * 2 * d * 2 + B * H * 2 * d * 2
+        attn = "attn_decode_split_kernel"
+    else:
+        pairs = sum(min(t + 1, window) for t in range(T))
+        by, attn = T * (H + G) * 2 * d * 2, "pt::attn_prefill_tc_kernel"
+    return {attn: [layers * by, layers * pairs * H * 4.0 * d],
+            "add_rmsnorm_vec_kernel": [(2 * layers + 1) * rows * W * (3 * 4 + 2), 0.0],
+            "swiglu_bf16x8_kernel": [layers * rows * ff * 6, 0.0],
+            "qkv_post_rows_kernel": [layers * rows * (H + 2 * G) * d * 6, 0.0]}
 
 
 def run_vizalix(args):
@@ -625,9 +643,10 @@ def run_vizalix(args):
                                                          vars(part).values() if isinstance(p, torch.Tensor)
                                                          and p.dtype == torch.bfloat16) / 1e6, 1),
                             "prefill_kernels": pf_kernels, "decode_kernels": dc_kernels}
-            if which == "vizalix":
+            if True:
                 for phase, table, dec in (("prefill", pf_kernels, False), ("decode", dc_kernels, True)):
-                    work = _vizalix_kernel_work(cfg, T, B, ctx, dec)
+                    work = (_vizalix_kernel_work(cfg, T, B, ctx, dec) if which == "vizalix"
+                            else _twin_kernel_work(size, window, T, B, ctx, dec, 10))
                     for name, (by, fl) in work.items():
                         if name in table:
                             floor_us = max(by / (pk["hbm_gbs"] * 1e9), fl / (pk["bf16_tflops"] * 1e12)) * 1e6
