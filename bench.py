@@ -461,8 +461,8 @@ def vizalix_config(size, window, vocab):
              "mixer": {"heads": H, "kv_heads": H, "dim": d, "vdim": d, "conv": 4, "decay_rank": 64, "gate_rank": 64}}
     attn = {"type": "attention", "mlp": mlp,
             "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "mask": {"size": window}, "scale": d ** -0.5,
-                      "softcap": 30.0, "rot": {"base": 250000.0, "dims": d // 2,
-                                               "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+                      "softcap": 50.0, "rot": {"base": 500000.0, "dims": d // 2,
+                                               "scaling": {"factor": 4.0, "low": 1.0, "high": 8.0, "original": 8192}}}}
     mamba = {"type": "mamba2", "mlp": mlp,
              "mixer": {"heads": 2 * H, "vdim": d // 2, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}}
     return {"architecture": "Vizalix", "vocab": vocab, "width": W, "norm": {"eps": 1e-6},
@@ -520,14 +520,16 @@ def _vizalix_kernel_work(cfg, T, B, ctx, decode):
             ch = 2 * m["kv_heads"] * d + H * e
             state = (B if decode else 1) * H * d * e * 4 * 2
             add("delta_scan_kernel", n * (rows * (ch + H * d + H + H * e) * 4 + state), n * rows * H * d * e * 6.0)
-            add("causal_conv_silu_kernel", n * rows * ch * 8, n * rows * ch * 8.0)
+            for name in ("causal_conv_silu_kernel", "causal_conv_silu_vec4_kernel"):
+                add(name, n * rows * ch * 8, n * rows * ch * 8.0)
             add("gated_group_rmsnorm_kernel", n * rows * H * e * (4 + 4 + 2), 0)
         elif L["type"] == "mamba2":
             H, P, N = m["heads"], m["vdim"], m["state"]
             ch = H * P + 2 * N
             state = (B if decode else 1) * H * N * P * 4 * 2
             add("ssd_scan_kernel", n * (rows * (ch + H + H * P) * 4 + state), n * rows * H * N * P * 4.0)
-            add("causal_conv_silu_kernel", n * rows * ch * 8, n * rows * ch * 8.0)
+            for name in ("causal_conv_silu_kernel", "causal_conv_silu_vec4_kernel"):
+                add(name, n * rows * ch * 8, n * rows * ch * 8.0)
             add("gated_group_rmsnorm_kernel", n * rows * H * P * (4 + 4 + 2), 0)
         else:
             H, G, d, e, win = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["mask"]["size"]
@@ -542,7 +544,8 @@ def _vizalix_kernel_work(cfg, T, B, ctx, decode):
                 add(name, n * by, n * pairs * H * (2.0 * d + 2.0 * e + 2.0 * H))
             add("rope_store_kernel", n * rows * (H * d + G * (d + e)) * 6, 0)
         add("add2_rmsnorm_scalar_kernel", n * rows * W * (4 * 4 + 2 * 2), 0)
-        add("geglu_tanh_kernel", n * rows * L["mlp"]["ff"] * 6, 0)
+        for name in ("geglu_tanh_kernel", "geglu_tanh_bf16x8_kernel"):
+            add(name, n * rows * L["mlp"]["ff"] * 6, 0)
     return out
 
 

@@ -69,6 +69,29 @@ __global__ void geglu_tanh_kernel(const AT* __restrict__ gu, AT* __restrict__ ou
     }
 }
 
+// bfloat16 rows with I a multiple of 8: 16 bytes per load and store
+__global__ void geglu_tanh_bf16x8_kernel(const uint4* __restrict__ gu, uint4* __restrict__ out, int64_t total_vec,
+                                         int Iv) {
+    wait_for_earlier_kernels();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_vec;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / Iv;
+        const int i = (int)(idx - t * Iv);
+        const uint4 gv = __ldg(gu + t * 2 * Iv + i);
+        const uint4 uv = __ldg(gu + t * 2 * Iv + Iv + i);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 r;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            r2[j] = __floats2bfloat162_rn(gelu_tanh_f(g.x) * u.x, gelu_tanh_f(g.y) * u.y);
+        }
+        out[idx] = r;
+    }
+}
+
 template <typename AT>
 __global__ void __launch_bounds__(256)
 concat_cast_kernel(const float* __restrict__ hidden, const float* __restrict__ a, const float* __restrict__ b,
@@ -114,6 +137,15 @@ int mi_add2_rmsnorm_scalar(float* hidden, const float* a, const float* b, const 
 int mi_geglu_tanh(const void* gu, void* out, int adtype, int64_t T, int I, cudaStream_t stream) {
     const int64_t total = T * I;
     if (total <= 0) return kOk;
+    if (adtype == kBF16 && I % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const int64_t total_vec = total / 8;
+        int64_t vblocks = (total_vec + 255) / 256;
+        if (vblocks > 148 * 16) vblocks = 148 * 16;
+        launch_dependent(geglu_tanh_bf16x8_kernel, dim3((int)vblocks), dim3(256), 0, stream, (const uint4*)gu,
+                         (uint4*)out, total_vec, I / 8);
+        return finish_launch("geglu_tanh");
+    }
     int64_t blocks = (total + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
     MI_DISPATCH_1(adtype, AT,

@@ -38,7 +38,7 @@ def runner_for(folder, dtype, **kw):
     from mini_infer_b200.engine.loading import load_model
     from mini_infer_b200.engine.step import ModelRunner
     model, rt, _ = load_model(folder, dtype, "cuda:0")
-    args = dict(page_size=8, num_pages=40, max_requests=4, max_tokens_per_step=256, max_context=320)
+    args = dict(page_size=8, num_pages=40, max_requests=4, max_tokens_per_step=256, max_context=352)
     args.update(kw)
     return ModelRunner(model, rt, **args)
 

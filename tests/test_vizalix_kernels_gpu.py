@@ -30,16 +30,19 @@ def batch_meta(lengths, slots):
     return i32(starts), i32(req), i32(slots)
 
 
-@pytest.mark.parametrize("taps,C,bias", [(4, 70, False), (2, 33, True), (1, 8, True), (8, 300, False)])
-def test_causal_conv_in_portions_and_batches(taps, C, bias):
+@pytest.mark.parametrize("taps,C,bias,aligned", [(4, 70, False, False), (2, 33, True, False), (1, 8, True, False),
+                                                 (8, 300, False, False), (4, 72, True, True), (3, 1024, False, True)])
+def test_causal_conv_in_portions_and_batches(taps, C, bias, aligned):
+    """``aligned``: rows, columns and state section start on 16-byte boundaries (the four-channel form)."""
     g = torch.Generator().manual_seed(taps * 100 + C)
     lens = [37, 5, 1, 19]
-    ld, col0 = C + 11, 7
+    ld, col0 = (C + 12, 8) if aligned else (C + 11, 7)
+    off = 8 if aligned else 5
     xs = [torch.randn(n, ld, generator=g) for n in lens]
     w = torch.randn(C, taps, generator=g)
     b = torch.randn(C, generator=g) if bias else None
     want = [pv.short_conv_silu(x[:, col0:col0 + C].double(), w.double(), None if b is None else b.double()) for x in xs]
-    state = torch.zeros(6, 5 + (taps - 1) * C, device=DEV)
+    state = torch.zeros(6, off + (taps - 1) * C, device=DEV)
     slots = [4, 0, 2, 5]
     fed = [0] * 4
     got = [torch.zeros(n, C) for n in lens]
@@ -49,7 +52,7 @@ def test_causal_conv_in_portions_and_batches(taps, C, bias):
         ns = [cuts[i][r] for i in live]
         x = torch.cat([xs[i][fed[i]:fed[i] + n] for i, n in zip(live, ns)]).to(DEV)
         qs, req, sl = batch_meta(ns, [slots[i] for i in live])
-        out = F().causal_conv_silu(x, col0, C, w.to(DEV), None if b is None else b.to(DEV), state, 5, qs, req, sl).cpu()
+        out = F().causal_conv_silu(x, col0, C, w.to(DEV), None if b is None else b.to(DEV), state, off, qs, req, sl).cpu()
         o = 0
         for i, n in zip(live, ns):
             got[i][fed[i]:fed[i] + n] = out[o:o + n]
@@ -62,8 +65,8 @@ def test_causal_conv_in_portions_and_batches(taps, C, bias):
         n = min(taps - 1, lens[i])
         if n:
             tail[taps - 1 - n:] = xs[i][lens[i] - n:, col0:col0 + C]
-        assert torch.equal(state[slots[i], 5:].cpu().view(taps - 1, C), tail)
-    assert float(state[:, :5].abs().max()) == 0.0 and float(state[1].abs().max()) == 0.0
+        assert torch.equal(state[slots[i], off:].cpu().view(taps - 1, C), tail)
+    assert float(state[:, :off].abs().max()) == 0.0 and float(state[1].abs().max()) == 0.0
 
 
 def _delta_inputs(T, H, G, d, e, seed):
@@ -385,7 +388,7 @@ def run_attention_tc(q, k, v, talk, window, scale, cap, cuts, page_size=8):
     return torch.cat(outs)
 
 
-@pytest.mark.parametrize("H,G,d,e,window", [(16, 4, 64, 128, 40), (8, 4, 128, 128, 300), (4, 2, 16, 64, 9), (24, 8, 32, 64, 64),
+@pytest.mark.parametrize("H,G,d,e,window", [(16, 4, 64, 128, 40), (8, 2, 128, 128, 300), (4, 2, 16, 64, 9), (24, 8, 32, 64, 64),
                                             (5, 1, 48, 64, 17), (3, 3, 16, 128, 0),
                                             # more heads than one block finishes: two and three blocks share a query tile
                                             (24, 8, 128, 128, 150), (40, 8, 32, 64, 33), (18, 3, 16, 128, 70)])
