@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(256)
 rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                   const int* __restrict__ slot_mapping, AT* __restrict__ q_out, AT* __restrict__ k_cache,
                   AT* __restrict__ v_cache, int nh, int nkv, int dk, int dv, int rot_dim, int page_size) {
+    extern __shared__ float trig[];                 // cos and sin of this token's rot_dim / 2 angles
     wait_for_earlier_kernels();
     const int t = blockIdx.x;
     const float* row = qkv + (int64_t)t * ((int64_t)(nh + nkv) * dk + (int64_t)nkv * dv);
@@ -30,13 +31,19 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
     const int slot = slot_mapping ? slot_mapping[t] : -1;
     const int half = rot_dim / 2;
     const int nqk = (nh + nkv) * dk;
+    // the angles depend on the position and the pair only: once per token, not once per head
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = pos * inv_freq[i];
+        trig[i] = cosf(ang);
+        trig[half + i] = sinf(ang);
+    }
+    __syncthreads();
     for (int idx = threadIdx.x; idx < nqk; idx += blockDim.x) {
         const int head = idx / dk, c = idx - head * dk;
         float v = row[idx];
         if (c < rot_dim) {
             const int i = c < half ? c : c - half;
-            const float ang = pos * inv_freq[i];
-            const float cs = cosf(ang), sn = sinf(ang);
+            const float cs = trig[i], sn = trig[half + i];
             const float other = row[idx + (c < half ? half : -half)];
             v = c < half ? v * cs - other * sn : v * cs + other * sn;
         }
@@ -307,7 +314,7 @@ int mi_rope_store(const float* qkv, const int* positions, const float* inv_freq,
         return kBadShape;
     }
     MI_DISPATCH_1(adtype, AT,
-        launch_dependent(rope_store_kernel<AT>, dim3(T), dim3(256), 0, stream, qkv, positions, inv_freq,
+        launch_dependent(rope_store_kernel<AT>, dim3(T), dim3(256), sizeof(float) * (rot_dim > 0 ? rot_dim : 1), stream, qkv, positions, inv_freq,
                          slot_mapping, (AT*)q_out, (AT*)k_cache, (AT*)v_cache, nh, nkv, dk, dv, rot_dim, page_size));
     return finish_launch("rope_store");
 }

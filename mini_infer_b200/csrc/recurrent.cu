@@ -48,7 +48,8 @@ causal_conv_silu_kernel(const float* __restrict__ x, int ldx, const WT* __restri
 #pragma unroll
     for (int j = 0; j < kMaxTaps; ++j) wt[j] = j < taps ? to_float(w[(int64_t)c * taps + j]) : 0.f;
     const float bv = bias ? to_float(bias[c]) : 0.f;
-    for (int t = blockIdx.y; t < T; t += gridDim.y) {
+    const int per = (T + gridDim.y - 1) / gridDim.y;         // a block's tokens are neighbours in time: their inputs overlap
+    for (int t = blockIdx.y * per; t < min(T, (blockIdx.y + 1) * per); ++t) {
         const int b = req_of_token[t];
         const int i = t - q_start[b];
         const float* st = state + (int64_t)state_slot[b] * state_stride;
@@ -83,7 +84,8 @@ causal_conv_silu_vec4_kernel(const float* __restrict__ x, int ldx, const WT* __r
         for (int j = 0; j < kMaxTaps; ++j) wt[k][j] = j < taps ? to_float(w[(int64_t)(c + k) * taps + j]) : 0.f;
     float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
     if (bias) bv = make_float4(to_float(bias[c]), to_float(bias[c + 1]), to_float(bias[c + 2]), to_float(bias[c + 3]));
-    for (int t = blockIdx.y; t < T; t += gridDim.y) {
+    const int per = (T + gridDim.y - 1) / gridDim.y;
+    for (int t = blockIdx.y * per; t < min(T, (blockIdx.y + 1) * per); ++t) {
         const int b = req_of_token[t];
         const int i = t - q_start[b];
         const float* st = state + (int64_t)state_slot[b] * state_stride;
@@ -450,26 +452,54 @@ template <typename AT, typename WT>
 __global__ void __launch_bounds__(256)
 gated_group_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ gate, int ld_gate,
                            const WT* __restrict__ w, int wlen, AT* __restrict__ out, int n, int gs, int mode,
-                           float eps) {
+                           float eps, bool vec) {
     __shared__ float scratch[32];
     wait_for_earlier_kernels();
     const int t = blockIdx.x, c0 = blockIdx.y * gs;
     const float* yr = y + (int64_t)t * n + c0;
     const float* gr = gate + (int64_t)t * ld_gate + c0;
+    AT* orow = out + (int64_t)t * n + c0;
+    // vec: every row's groups start on 16-byte boundaries (decided for the whole launch from the sizes, so that
+    // the order of a row's sum does not depend on where the row stands in a step): four floats per access
     float ss = 0.f;
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-        float v = yr[i];
-        if (mode == 0) v *= silu_f(gr[i]);
-        ss += v * v;
+    if (vec) {
+        for (int i = 4 * threadIdx.x; i < gs; i += 4 * blockDim.x) {
+            float4 v = *reinterpret_cast<const float4*>(yr + i);
+            if (mode == 0) {
+                const float4 g = *reinterpret_cast<const float4*>(gr + i);
+                v.x *= silu_f(g.x); v.y *= silu_f(g.y); v.z *= silu_f(g.z); v.w *= silu_f(g.w);
+            }
+            ss += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+            float v = yr[i];
+            if (mode == 0) v *= silu_f(gr[i]);
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, scratch);
     const float rr = 1.0f / sqrtf(ss / (float)gs + eps);
-    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
-        float v = yr[i];
-        if (mode == 0) v *= silu_f(gr[i]);
-        v = v * rr * to_float(w[(c0 + i) % wlen]);
-        if (mode == 1) v *= sigmoid_f(gr[i]);
-        out[(int64_t)t * n + c0 + i] = from_float<AT>(v);
+    if (vec) {
+        for (int i = 4 * threadIdx.x; i < gs; i += 4 * blockDim.x) {
+            float4 v = *reinterpret_cast<const float4*>(yr + i);
+            const float4 g = *reinterpret_cast<const float4*>(gr + i);
+            if (mode == 0) { v.x *= silu_f(g.x); v.y *= silu_f(g.y); v.z *= silu_f(g.z); v.w *= silu_f(g.w); }
+            const int wi = (c0 + i) % wlen;
+            v.x *= rr * to_float(w[wi]); v.y *= rr * to_float(w[wi + 1]);
+            v.z *= rr * to_float(w[wi + 2]); v.w *= rr * to_float(w[wi + 3]);
+            if (mode == 1) { v.x *= sigmoid_f(g.x); v.y *= sigmoid_f(g.y); v.z *= sigmoid_f(g.z); v.w *= sigmoid_f(g.w); }
+            orow[i] = from_float<AT>(v.x); orow[i + 1] = from_float<AT>(v.y);
+            orow[i + 2] = from_float<AT>(v.z); orow[i + 3] = from_float<AT>(v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+            float v = yr[i];
+            if (mode == 0) v *= silu_f(gr[i]);
+            v = v * rr * to_float(w[(c0 + i) % wlen]);
+            if (mode == 1) v *= sigmoid_f(gr[i]);
+            orow[i] = from_float<AT>(v);
+        }
     }
 }
 
@@ -489,7 +519,10 @@ int mi_causal_conv_silu(const float* x, int ldx, const void* w, const void* bias
     }
     if (B > 65535) { set_last_error("causal convolution: %d requests exceed the grid limit", B); return kBadShape; }
     const int cb = (C + 255) / 256;
-    int ty = T < 4096 ? T : 4096;
+    // ranges of about 16 tokens per block (fewer when that leaves SMs idle)
+    int ty = (T + 15) / 16;
+    if (ty * cb < 296) ty = T < (296 + cb - 1) / cb ? T : (296 + cb - 1) / cb;
+    if (ty > 65535) ty = 65535;
     const bool vec4 = C % 4 == 0 && ldx % 4 == 0 && ld_out % 4 == 0 && state_stride % 4 == 0 &&
                       ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(state)) & 15) == 0;
     if (vec4) {
@@ -570,11 +603,14 @@ int mi_gated_group_rmsnorm(const float* y, const float* gate, int ld_gate, const
         return kBadShape;
     }
     const int gs = n / groups;
+    const bool vec = gs % 4 == 0 && wlen % 4 == 0 && n % 4 == 0 && ld_gate % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gate)) & 15) == 0;
+    const int work = vec ? gs / 4 : gs;      // a thread takes four floats where it can
     int threads = 32;
-    while (threads < gs && threads < 256) threads *= 2;
+    while (threads < work && threads < 256) threads *= 2;
     MI_DISPATCH_2(adtype, AT, wdtype, WT,
         launch_dependent(gated_group_rmsnorm_kernel<AT, WT>, dim3(T, groups), dim3(threads), 0, stream, y, gate,
-                         ld_gate, (const WT*)w, wlen, (AT*)out, n, gs, mode, eps));
+                         ld_gate, (const WT*)w, wlen, (AT*)out, n, gs, mode, eps, vec));
     return finish_launch("gated_group_rmsnorm");
 }
 
