@@ -17,6 +17,7 @@ import torch
 
 from ..config.registry import register_part
 from ..ops import functional as F
+from .tuning import TUNING
 from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, StepContext, TensorDecl, TensorSum,
                    apply_norm, linear, split_sum)
 
@@ -101,6 +102,7 @@ class ParallelResidual(Block):
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.has_ff = bool(self.params.get("feed_forward", True))
+        self._side_stream = None
         self.roles = {"mixer_norm": "norm", "mixer": "mixer"}
         if self.has_ff:
             self.roles.update({"feed_forward_norm": "norm", "feed_forward": "feed_forward"})
@@ -117,8 +119,21 @@ class ParallelResidual(Block):
         else:
             x1 = apply_norm(n1, hidden, pending)
             x2 = apply_norm(n2, hidden, None)
+        if not (TUNING.parallel_residual_two_streams and x1.is_cuda):
+            y = layer.mixer.forward(x1, ctx, caches.get("mixer"))
+            return TensorSum(y, layer.feed_forward.forward(x2, ctx))
+        # the two branches share nothing but the residual they read: the feed-forward goes to a second stream
+        main = torch.cuda.current_stream()
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(device=x1.device)
+        side = self._side_stream
+        side.wait_stream(main)
+        x2.record_stream(side)
+        with torch.cuda.stream(side):
+            f = layer.feed_forward.forward(x2, ctx)
+        f.record_stream(main)
         y = layer.mixer.forward(x1, ctx, caches.get("mixer"))
-        f = layer.feed_forward.forward(x2, ctx)
+        main.wait_stream(side)
         return TensorSum(y, f)
 
     def prefetch_layer(self, layer: BuiltLayer, ctx: StepContext, caches) -> None:

@@ -93,6 +93,11 @@ class Tuning:
     # through while it grows and shrinks request by request.
     decode_graph_exact_batch_max: int = 16
 
+    # A block whose mixer and feed-forward read the same residual (``parallel_residual``) runs the feed-forward on
+    # a second stream beside the mixer: a recurrent mixer walks a prompt with a few warps per SM and the
+    # feed-forward's products fill the rest; in a decode step the two chains of small kernels run side by side.
+    parallel_residual_two_streams: bool = True
+
     def decode_graph_batch(self, num_requests: int) -> int:
         if num_requests <= self.decode_graph_exact_batch_max:
             return num_requests
