@@ -37,7 +37,7 @@ __device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2
 
 constexpr int kTcQ = 16;          // queries per block
 constexpr int kTcWarps = 8;
-constexpr int kTcSplitKeys = 128; // keys per block of a split step
+constexpr int kTcSplitKeys = 64;  // keys per block of a split step
 
 template <int HPW, int NT, int KT>      // heads per warp, value size / 8, keys per tile
 __global__ void __launch_bounds__(256, 1)
