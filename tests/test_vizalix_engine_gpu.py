@@ -53,7 +53,7 @@ def check(got, ref, tol):
     return worst
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R", "S"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "S", "T"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_every_cutting_against_the_plain_model(models, name, dtype):
     folder, cfg, w = models[name]
@@ -69,6 +69,9 @@ def test_every_cutting_against_the_plain_model(models, name, dtype):
         check(got, ref, TOL[dtype])
         results.append(got)
         assert runner.cache.used_pages() == [0] * len(runner.cache.pools)
+    if name == "T" and dtype == "bfloat16":
+        mixers = [l.parts["mixer"] for l in runner.model.layers if "mixer" in l.parts]
+        assert [m._tensor_cores for m in mixers if hasattr(m, "_tensor_cores")] == [True, True]
     if dtype == "float32":
         # the 32-bit path gives the same bits however the work was cut and batched
         for other in results[1:5]:

@@ -70,10 +70,26 @@ CONFIG_R = {
     "loop": {"start": 0, "stop": 4, "times": 2},
 }
 
+# attention shapes that the bfloat16 path takes to the tensor cores (value size 64, key size a multiple of 16),
+# once with more heads than one block finishes
+CONFIG_T = {
+    "architecture": "Vizalix", "vocab": 160, "width": 64, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "mamba2", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": {"heads": 2, "vdim": 16, "state": 16, "groups": 2, "norm_groups": 1, "conv": 4}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": _attn(4, 2, 32, 64, 40, rot={"base": 10000.0, "dims": 16, "scaling": {"factor": 8.0, "low": 1.0, "high": 2.0, "original": 48}}, cap=20.0)},
+        {"type": "channel_delta", "mlp": {"kind": "dense", "ff": 64},
+         "mixer": {"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 32, "conv": 4, "decay_rank": 8, "gate_rank": 8}},
+        {"type": "attention", "mlp": None, "mixer": _attn(36, 4, 16, 64, 23, cap=8.0)},
+    ],
+    "loop": {"start": 1, "stop": 4, "times": 2},
+}
+
 # one pass of a "loop" (the merge of the embedding still runs once)
 CONFIG_S = dict(CONFIG_Q, loop={"start": 2, "stop": 3, "times": 1})
 
-CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R, "S": CONFIG_S}
+CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R, "S": CONFIG_S, "T": CONFIG_T}
 
 
 def make_weights(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
