@@ -385,11 +385,9 @@ class ModelRunner:
         from ..parts.tuning import TUNING
         return min(TUNING.decode_graph_batch(num_requests), self.max_requests, self.max_tokens)
 
-    def _decode_with_graph(self, ctx: StepContext, logit_rows: Optional[torch.Tensor],
-                           chunk: bool = False) -> Optional[torch.Tensor]:
-        """Replay (or first capture) the forward pass for this batch size and context-length bucket.
-        The captured pass reads the same staging views every time and is launched for the longest
-        context of its bucket, so only the data in the staging buffer changes between replays."""
+    def _graph_key(self, ctx: StepContext, logit_rows: Optional[torch.Tensor], chunk: bool = False) -> tuple:
+        """The key of the captured pass that serves this step; sets ``ctx.max_kv_len`` to the longest context
+        of the pass's bucket (calling it twice changes nothing more)."""
         B = ctx.num_requests
         if chunk:
             # no launch shape of a prompt portion follows the context length
@@ -402,9 +400,16 @@ class ModelRunner:
             while bucket < ctx.max_kv_len:
                 bucket *= 2
             ctx.max_kv_len = min(bucket, self.max_context)
+        return (B, ctx.max_kv_len, tuple(p.capture_key() for p in self._keyed_parts),
+                (ctx.num_tokens, logit_rows is not None) if chunk else None)
+
+    def _decode_with_graph(self, ctx: StepContext, logit_rows: Optional[torch.Tensor],
+                           chunk: bool = False) -> Optional[torch.Tensor]:
+        """Replay (or first capture) the forward pass for this batch size and context-length bucket.
+        The captured pass reads the same staging views every time and is launched for the longest
+        context of its bucket, so only the data in the staging buffer changes between replays."""
         parts = self._keyed_parts
-        key = (B, ctx.max_kv_len, tuple(p.capture_key() for p in parts),
-               (ctx.num_tokens, logit_rows is not None) if chunk else None)
+        key = self._graph_key(ctx, logit_rows, chunk)
         if key not in self._graphs:
             # The warm-up pass (library workspaces, lazy initialisation) runs the step for real: what it
             # writes into the paged caches is written again by the replay, but a per-request state would
@@ -444,8 +449,11 @@ class ModelRunner:
         # What a failed step wrote into the paged caches lies beyond every request's committed tokens and
         # is written again; a per-request state is updated in place, so the entries' slots are kept aside
         # and put back if the forward pass fails.
+        # (A replay of a pass that exists launches no Python of the parts: nothing in it can raise on the host,
+        # so the copy, megabytes per request for recurrent mixers, is left out there.)
         saved = None
-        if self.state_tensors:
+        replay = decode_graph and self._graph_key(ctx, logit_rows) in self._graphs
+        if self.state_tensors and not replay:
             slots = torch.as_tensor(ctx.host_state_slot, dtype=torch.long, device=self.rt.device)
             saved = (slots, [st.index_select(0, slots) for st in self.state_tensors])
         try:
