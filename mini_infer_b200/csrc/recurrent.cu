@@ -155,6 +155,19 @@ __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.com
 // all groups but the most recent one have landed
 __device__ __forceinline__ void copy_async_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 
+// loads from shared memory by its own 32-bit addresses (the delta rule's walk: 7 % shorter than through pointers;
+// the Mamba-2 walk, with fewer loads per token, lost 4 % and keeps its pointers)
+__device__ __forceinline__ float4 shared_f4(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ float shared_f1(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(a) : "memory");
+    return v;
+}
+
 // row of S that element (m, x) of lane r holds
 __device__ __forceinline__ int scan_row(int r, int m, int x) { return 4 * (r + kScanLanes * m) + x; }
 
@@ -245,6 +258,8 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, con
         const int nc = min(kScanChunk, n - c0);
         const float* rows = sm + which * kBuf;
         const float* vs = rows + kScanChunk * ROW;
+        const uint32_t rows_a = static_cast<uint32_t>(__cvta_generic_to_shared(rows));
+        const uint32_t vs_a = static_cast<uint32_t>(__cvta_generic_to_shared(vs));
         if (c0 + kScanChunk < n) fetch(c0 + kScanChunk, sm + (which ^ 1) * kBuf);     // read last two syncs ago
         copy_async_commit();
         copy_async_wait_but_one();
@@ -257,23 +272,24 @@ delta_scan_kernel(const float* __restrict__ qkv, int ld_qkv, int64_t v_col0, con
             for (int u4 = 0; u4 < 4; ++u4) {
                 const int tt = t4 + u4;
                 if (tt < nc) {
-                    const float4* qq = reinterpret_cast<const float4*>(rows + tt * ROW);
-                    const float4* kq = qq + DP / 4;
-                    const float4* gq = kq + DP / 4;
+                    const uint32_t qa = rows_a + (uint32_t)(tt * ROW + 4 * r) * 4u;       // this lane's first q
+                    float4 k4[MV];
                     float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
                     for (int m = 0; m < MV; ++m) {
-                        const float4 g4 = gq[r + kScanLanes * m], k4 = kq[r + kScanLanes * m];
+                        const float4 g4 = shared_f4(qa + (2 * DP + 4 * kScanLanes * m) * 4);
+                        k4[m] = shared_f4(qa + (DP + 4 * kScanLanes * m) * 4);
                         s[4 * m] *= g4.x; s[4 * m + 1] *= g4.y; s[4 * m + 2] *= g4.z; s[4 * m + 3] *= g4.w;
-                        a0 += s[4 * m] * k4.x; a1 += s[4 * m + 1] * k4.y; a2 += s[4 * m + 2] * k4.z; a3 += s[4 * m + 3] * k4.w;
+                        a0 += s[4 * m] * k4[m].x; a1 += s[4 * m + 1] * k4[m].y; a2 += s[4 * m + 2] * k4[m].z; a3 += s[4 * m + 3] * k4[m].w;
                     }
                     const float acc = lanes_sum((a0 + a1) + (a2 + a3));
-                    const float u = rows[tt * ROW + 3 * DP] * (vs[tt * kScanCols + lc] - acc);
+                    const float u = shared_f1(rows_a + (uint32_t)(tt * ROW + 3 * DP) * 4u) *
+                                    (shared_f1(vs_a + (uint32_t)(tt * kScanCols + lc) * 4u) - acc);
                     float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
                     for (int m = 0; m < MV; ++m) {
-                        const float4 k4 = kq[r + kScanLanes * m], q4 = qq[r + kScanLanes * m];
-                        s[4 * m] += k4.x * u; s[4 * m + 1] += k4.y * u; s[4 * m + 2] += k4.z * u; s[4 * m + 3] += k4.w * u;
+                        const float4 q4 = shared_f4(qa + (4 * kScanLanes * m) * 4);
+                        s[4 * m] += k4[m].x * u; s[4 * m + 1] += k4[m].y * u; s[4 * m + 2] += k4[m].z * u; s[4 * m + 3] += k4[m].w * u;
                         o0 += s[4 * m] * q4.x; o1 += s[4 * m + 1] * q4.y; o2 += s[4 * m + 2] * q4.z; o3 += s[4 * m + 3] * q4.w;
                     }
                     o_part[u4] = (o0 + o1) + (o2 + o3);
