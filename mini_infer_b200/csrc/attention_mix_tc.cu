@@ -35,6 +35,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // library functions cost thirty to forty instructions apiece, a third of a key tile's work
 __device__ __forceinline__ float fast_tanh(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
 
+__device__ __forceinline__ void tile_copy_16(void* smem_dst, const void* src) {
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void tile_copy_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void tile_copy_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+
 constexpr int kTcQ = 16;          // queries per block
 constexpr int kTcWarps = 8;
 constexpr int kTcSplitKeys = 64;  // keys per block of a split step
@@ -63,13 +70,13 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int r0 = lane >> 2, c2 = (lane & 3) * 2;
     const int rep = H / G;
     const int dkp = dk + 8, dvp = DV + 8;
-    const int kv_stride = dkp > dvp ? dkp : dvp;
     float* S1 = reinterpret_cast<float*>(smem_raw);                       // [H][16][SP]
     float* S2 = S1 + H * kTcQ * SP;                                       // [HG][16][SP], heads of this block
     float* Mx = S2 + HG * kTcQ * SP;                                      // [H][H]
-    int* slot_of = reinterpret_cast<int*>(Mx + ((H * H + 3) & ~3));       // [KT]
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(slot_of + KT + ((4 - KT % 4) % 4));   // [H][16][dkp]
-    __nv_bfloat16* KV = Qs + (size_t)H * kTcQ * dkp;                      // [G][KT][kv_stride]
+    int* slots = reinterpret_cast<int*>(Mx + ((H * H + 3) & ~3));         // [2][KT]: this tile's and the next one's
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(slots + 2 * KT); // [H][16][dkp]
+    __nv_bfloat16* Kb = Qs + (size_t)H * kTcQ * dkp;                      // [G][KT][dkp]
+    __nv_bfloat16* Vb = Kb + (size_t)G * KT * dkp;                        // [G][KT][dvp]
 
     const int nq = min(kTcQ, q_len - qt * kTcQ);
     const int p_lo = kvl - q_len + qt * kTcQ;
@@ -109,8 +116,10 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int* table = block_table + (size_t)b * max_pages;
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
-    for (int kt = k_begin; kt < k_end; kt += KT) {
-        __syncthreads();
+    // Keys and values travel a step ahead of their use (cp.async): the values of a tile are asked for before its
+    // scores are formed, the keys of the next tile as soon as the scores have left the key buffer.
+    constexpr int vchunks = DV / 8;
+    auto find_slots = [&](int kt, int* slot_of) {
         if (tid < KT) {
             const int kj = kt + tid;
             int s = -1;
@@ -120,17 +129,47 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             }
             slot_of[tid] = s;
         }
-        __syncthreads();
+    };
+    auto fetch_keys = [&](const int* slot_of) {
         for (int idx = tid; idx < G * KT * qchunks; idx += 256) {
             const int c8 = idx % qchunks, j = (idx / qchunks) % KT, g = idx / (qchunks * KT);
             const int s = slot_of[j];
-            uint4 v = make_uint4(0, 0, 0, 0);
+            __nv_bfloat16* dst = Kb + ((size_t)g * KT + j) * dkp + c8 * 8;
             if (s >= 0) {
                 const int page = s / page_size, off = s - page * page_size;
-                v = *reinterpret_cast<const uint4*>(k_cache + (((size_t)page * G + g) * page_size + off) * dk + c8 * 8);
+                tile_copy_16(dst, k_cache + (((size_t)page * G + g) * page_size + off) * dk + c8 * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
-            *reinterpret_cast<uint4*>(KV + ((size_t)g * KT + j) * kv_stride + c8 * 8) = v;
         }
+    };
+    auto fetch_values = [&](const int* slot_of) {
+        for (int idx = tid; idx < G * KT * vchunks; idx += 256) {
+            const int c8 = idx % vchunks, j = (idx / vchunks) % KT, g = idx / (vchunks * KT);
+            const int s = slot_of[j];
+            __nv_bfloat16* dst = Vb + ((size_t)g * KT + j) * dvp + c8 * 8;
+            if (s >= 0) {
+                const int page = s / page_size, off = s - page * page_size;
+                tile_copy_16(dst, v_cache + (((size_t)page * G + g) * page_size + off) * DV + c8 * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    if (k_begin < k_end) {
+        find_slots(k_begin, slots);
+        __syncthreads();
+        fetch_keys(slots);
+    }
+    tile_copy_commit();
+    int which = 0;
+    for (int kt = k_begin; kt < k_end; kt += KT, which ^= 1) {
+        const int* slot_of = slots + which * KT;
+        __syncthreads();                         // the tile before has left the value buffer and its scores
+        fetch_values(slot_of);
+        tile_copy_commit();
+        if (kt + KT < k_end) find_slots(kt + KT, slots + (which ^ 1) * KT);
+        tile_copy_wait_but_one();                // this tile's keys
         __syncthreads();
         // ---- scores of all heads ----
         for (int h = warp; h < H; h += kTcWarps) {
@@ -142,7 +181,7 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
                     for (int x = 0; x < 4; ++x) c[nt][x] = 0.f;
                 const __nv_bfloat16* qb = Qs + (size_t)h * kTcQ * dkp;
-                const __nv_bfloat16* kb = KV + (size_t)g * KT * kv_stride;
+                const __nv_bfloat16* kb = Kb + (size_t)g * KT * dkp;
                 for (int ks = 0; ks < dk; ks += 16) {
                     const uint32_t a0 = *reinterpret_cast<const uint32_t*>(qb + r0 * dkp + ks + c2);
                     const uint32_t a1 = *reinterpret_cast<const uint32_t*>(qb + (r0 + 8) * dkp + ks + c2);
@@ -150,7 +189,7 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                     const uint32_t a3 = *reinterpret_cast<const uint32_t*>(qb + (r0 + 8) * dkp + ks + 8 + c2);
 #pragma unroll
                     for (int nt = 0; nt < KT / 8; ++nt) {
-                        const __nv_bfloat16* kr = kb + (size_t)(nt * 8 + r0) * kv_stride + ks + c2;
+                        const __nv_bfloat16* kr = kb + (size_t)(nt * 8 + r0) * dkp + ks + c2;
                         const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr);
                         const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + 8);
                         mma_bf16_16816(c[nt], a0, a1, a2, a3, b0, b1);
@@ -168,18 +207,9 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             }
         }
         __syncthreads();
-        // ---- V over K; mix and mask ----
-        constexpr int vchunks = DV / 8;
-        for (int idx = tid; idx < G * KT * vchunks; idx += 256) {
-            const int c8 = idx % vchunks, j = (idx / vchunks) % KT, g = idx / (vchunks * KT);
-            const int s = slot_of[j];
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (s >= 0) {
-                const int page = s / page_size, off = s - page * page_size;
-                v = *reinterpret_cast<const uint4*>(v_cache + (((size_t)page * G + g) * page_size + off) * DV + c8 * 8);
-            }
-            *reinterpret_cast<uint4*>(KV + ((size_t)g * KT + j) * kv_stride + c8 * 8) = v;
-        }
+        // ---- the next tile's keys set off; mix and mask ----
+        if (kt + KT < k_end) fetch_keys(slots + (which ^ 1) * KT);
+        tile_copy_commit();
         for (int e = tid; e < kTcQ * KT; e += 256) {
             const int i = e / KT, j = e - i * KT;
             const int kj = kt + j, pos = p_lo + i;
@@ -209,6 +239,7 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                 }
             }
         }
+        tile_copy_wait_but_one();                // this tile's values
         __syncthreads();
         // ---- softmax and P.V of this block's heads ----
 #pragma unroll
@@ -254,14 +285,14 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                     acc[hh][nt][0] *= al0; acc[hh][nt][1] *= al0;
                     acc[hh][nt][2] *= al1; acc[hh][nt][3] *= al1;
                 }
-                const __nv_bfloat16* vb = KV + (size_t)g * KT * kv_stride;
+                const __nv_bfloat16* vb = Vb + (size_t)g * KT * dvp;
 #pragma unroll
                 for (int kk = 0; kk < KT / 16; ++kk) {
                     const uint32_t a0 = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
                     const uint32_t a1 = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
                     const uint32_t a2 = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
                     const uint32_t a3 = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
-                    const __nv_bfloat16* vrow = vb + (size_t)(kk * 16 + (lane & 15)) * kv_stride;
+                    const __nv_bfloat16* vrow = vb + (size_t)(kk * 16 + (lane & 15)) * dvp;
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         uint32_t b0, b1;
@@ -337,9 +368,8 @@ attn_mix_merge_kernel(const float* __restrict__ part_o, const float* __restrict_
 
 static size_t tc_smem(int H, int HG, int G, int dk, int dv, int kt) {
     const int dkp = dk + 8, dvp = dv + 8;
-    const int kvs = dkp > dvp ? dkp : dvp;
-    return (size_t)(H + HG) * kTcQ * (kt + 1) * 4 + (size_t)((H * H + 3) & ~3) * 4 + (size_t)(kt + 4) * 4 +
-           (size_t)H * kTcQ * dkp * 2 + (size_t)G * kt * kvs * 2 + 16;
+    return (size_t)(H + HG) * kTcQ * (kt + 1) * 4 + (size_t)((H * H + 3) & ~3) * 4 + (size_t)2 * kt * 4 +
+           (size_t)H * kTcQ * dkp * 2 + (size_t)G * kt * (dkp + dvp) * 2 + 16;
 }
 
 struct TcPlan { int kt, hgroups, hpw; };
