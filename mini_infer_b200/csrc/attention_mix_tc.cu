@@ -2,13 +2,15 @@
 //
 // A block owns 16 consecutive queries of one request with ALL heads: the scores of a (query, key) pair are
 // mixed over the heads before the softmax, so no head can be computed alone.  Per tile of KT keys:
-//   1. K tile of every key/value head into shared memory (16-byte loads)
+//   1. the tile's values are asked for (cp.async, 16 bytes a piece, a buffer of their own); its keys, asked for
+//      while the tile before was finished, have landed
 //   2. S_h = Q_h K_g^T with mma.sync m16n8k16 (warp w owns heads w, w + 8, ...), scaled, capped, to shared
 //      memory as float
-//   3. V tile over the K tile; meanwhile the mix over heads and the mask, pair by pair, into a second buffer
+//   3. the next tile's keys are asked for; meanwhile the mix over heads and the mask, pair by pair, into a
+//      second buffer
 //   4. running softmax in the layout of the A fragments (a row's maximum and sum live in a quad of lanes),
 //      O_h += P_h V_g with V fragments fetched by ldmatrix.trans from the row-major tile
-// Steps of one token per request are split over the keys (blocks of 128 keys write a partial maximum, sum
+// Steps of one token per request are split over the keys (blocks of 64 keys write a partial maximum, sum
 // and unnormalised output; a merge kernel finishes), since one block per request cannot pull a window of
 // keys from memory fast enough.
 //
