@@ -46,6 +46,11 @@ class CacheGroupSpec:
     def window(self) -> int:
         return int(self.need.window)
 
+    @property
+    def keep_first(self) -> int:
+        """Tokens at the start of a request that a window group keeps for good."""
+        return int(getattr(self.need, "keep_first", 0) or 0)
+
     def __getattr__(self, name):
         # geometry of the need (num_kv_heads, head_dim, ...) read through the group
         if name in ("need", "entries"):
@@ -188,7 +193,8 @@ class CacheManager:
                 first_needed = r.num_tokens - spec.window + 1     # oldest key the next query reads
                 dead = max(0, first_needed) // self.page_size      # pages wholly below it
                 table = r.tables[g]
-                for i in range(min(dead, len(table))):
+                kept = -(-spec.keep_first // self.page_size)       # pages that hold a token every query reads
+                for i in range(kept, min(dead, len(table))):
                     if table[i] >= 0:
                         self.pools[g].free(table[i])
                         table[i] = -1
@@ -207,7 +213,7 @@ class CacheManager:
         for g, spec in enumerate(self.groups):
             if spec.window > 0 and num_tokens < r.num_tokens:
                 first_needed = max(0, num_tokens - spec.window + 1) // self.page_size
-                if any(p < 0 for p in r.tables[g][first_needed:keep]):
+                if any(p < 0 for p in r.tables[g][first_needed:keep]):   # (kept first pages are never released)
                     raise ValueError(f"CacheManager.truncate: group {g} (window {spec.window}) has released pages "
                                      f"that a query at position {num_tokens} would read; a request can go back "
                                      f"only as far as its window has not moved on")

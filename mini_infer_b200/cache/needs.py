@@ -24,11 +24,13 @@ class PagedCacheNeed:
     """Per-token entries kept in pages.
 
     ``window = 0`` keeps every token's entry, ``window = W`` only the last ``W`` (older pages are given
-    back).  ``pages_fraction`` is the share of the engine's page budget that the group of this need gets
-    (1.0 = as many pages as a full-history group)."""
+    back) and, with ``keep_first = F``, the first ``F`` tokens of the request as well (their pages are never
+    given back while the request lives).  ``pages_fraction`` is the share of the engine's page budget that
+    the group of this need gets (1.0 = as many pages as a full-history group)."""
 
     window: int = 0
     pages_fraction: float = 1.0
+    keep_first: int = 0
 
     def tensors(self, page_size: int) -> List[PageTensor]:
         """The tensors of one layer, per page of ``page_size`` tokens."""
@@ -40,7 +42,8 @@ class PagedCacheNeed:
 
     def group_key(self) -> tuple:
         """Layers whose needs have the same key share a page pool and a block table per request."""
-        return (type(self).__name__, self.geometry(), int(self.window), float(self.pages_fraction))
+        return (type(self).__name__, self.geometry(), int(self.window), float(self.pages_fraction),
+                int(self.keep_first) if self.window > 0 else 0)
 
     def bytes_per_page(self, page_size: int, act_itemsize: int) -> int:
         total = 0
@@ -62,10 +65,27 @@ class KVNeed(PagedCacheNeed):
     window: int = 0
     pages_fraction: float = 1.0
     value_dim: int = 0
+    keep_first: int = 0
 
     def tensors(self, page_size: int) -> List[PageTensor]:
         return [("k", (self.num_kv_heads, page_size, self.head_dim), None),
                 ("v", (self.num_kv_heads, page_size, self.value_dim or self.head_dim), None)]
+
+
+@dataclass(frozen=True)
+class LatentNeed(PagedCacheNeed):
+    """One row per token that all heads share: a latent of ``rank`` numbers from which every head's key and
+    value are formed, followed by ``rot_dim`` numbers of a rotated key part: ``latent`` pages of
+    ``[1, page_size, rank + rot_dim]``."""
+
+    rank: int
+    rot_dim: int
+    window: int = 0
+    pages_fraction: float = 1.0
+    keep_first: int = 0
+
+    def tensors(self, page_size: int) -> List[PageTensor]:
+        return [("latent", (1, page_size, self.rank + self.rot_dim), None)]
 
 
 @dataclass(frozen=True)

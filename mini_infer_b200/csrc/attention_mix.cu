@@ -7,11 +7,15 @@
 //   k_cache [page, kv_head, page_size, dk]      v_cache [page, kv_head, page_size, dv]
 //
 // Masking is positional: key j is visible from the query at absolute position p iff j <= p and
-// (window == 0 or j > p - window).  Key tiles are aligned to absolute positions and every sum runs in an
+// (window == 0 or j > p - window or j < keep_first): behind a window the first keep_first keys of a request
+// stay visible, at their true positions.  A value row may lie inside a longer row of memory (`vrs`, the
+// distance between two tokens' value rows in elements): values that are the leading part of their keys are
+// read from the key cache itself.  Key tiles are aligned to absolute positions and every sum runs in an
 // order that depends on the model's sizes only, so the result does not depend on how a prompt was cut.
 //
-// rope_store: rotary encoding of the first rot_dim dimensions of every query and key head (dimension i
-// is paired with i + rot_dim/2), cache write of keys and values.
+// rope_store: optionally each query and key head divided by its root mean square and multiplied by a gain
+// per dimension (shared by the heads), then rotary encoding of the first rot_dim dimensions of every query
+// and key head (dimension i is paired with i + rot_dim/2), cache write of keys and values.
 
 #include "common.cuh"
 
@@ -22,8 +26,10 @@ template <typename AT>
 __global__ void __launch_bounds__(256)
 rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
                   const int* __restrict__ slot_mapping, AT* __restrict__ q_out, AT* __restrict__ k_cache,
-                  AT* __restrict__ v_cache, int nh, int nkv, int dk, int dv, int rot_dim, int page_size) {
+                  AT* __restrict__ v_cache, int nh, int nkv, int dk, int dv, int rot_dim, int page_size,
+                  const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps) {
     extern __shared__ float trig[];                 // cos and sin of this token's rot_dim / 2 angles
+    float* inv_rms = trig + (rot_dim > 0 ? rot_dim : 1);    // [nh + nkv], with head norms only
     wait_for_earlier_kernels();
     const int t = blockIdx.x;
     const float* row = qkv + (int64_t)t * ((int64_t)(nh + nkv) * dk + (int64_t)nkv * dv);
@@ -37,14 +43,30 @@ rope_store_kernel(const float* __restrict__ qkv, const int* __restrict__ positio
         trig[i] = cosf(ang);
         trig[half + i] = sinf(ang);
     }
+    const bool normed = q_gain != nullptr;
+    if (normed) {
+        // a warp per head; a lane adds its dimensions in ascending order, then the lanes are added: an order
+        // that depends on dk only
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+        for (int head = warp; head < nh + nkv; head += nwarps) {
+            float ss = 0.f;
+            for (int c = lane; c < dk; c += 32) { const float x = row[head * dk + c]; ss += x * x; }
+            ss = warp_sum(ss);
+            if (lane == 0) inv_rms[head] = 1.0f / sqrtf(ss / (float)dk + eps);
+        }
+    }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nqk; idx += blockDim.x) {
         const int head = idx / dk, c = idx - head * dk;
         float v = row[idx];
+        const float* gain = head < nh ? q_gain : k_gain;
+        if (normed) v = v * inv_rms[head] * gain[c];
         if (c < rot_dim) {
             const int i = c < half ? c : c - half;
             const float cs = trig[i], sn = trig[half + i];
-            const float other = row[idx + (c < half ? half : -half)];
+            const int co = c < half ? c + half : c - half;
+            float other = row[head * dk + co];
+            if (normed) other = other * inv_rms[head] * gain[co];
             v = c < half ? v * cs - other * sn : v * cs + other * sn;
         }
         if (head < nh) {
@@ -80,7 +102,7 @@ __global__ void __launch_bounds__(256)
 attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const AT* __restrict__ v_cache,
                 const float* __restrict__ mix, const int* __restrict__ block_table, const int* __restrict__ q_start,
                 const int* __restrict__ kv_len, AT* __restrict__ out, int H, int G, int dk, int dv, int page_size,
-                int max_pages, int window, float scale, float cap, int QT, int KT, int rpw) {
+                int max_pages, int window, float scale, float cap, int QT, int KT, int rpw, int keep_first, int vrs) {
     constexpr int RPW = MixCfg<AT, CPL>::RPW;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     wait_for_earlier_kernels();
@@ -131,13 +153,21 @@ attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const 
     k_begin = (k_begin / KT) * KT;
     const int k_end = min(kvl, p_hi + 1);
     const int* table = block_table + (int64_t)b * max_pages;
+    // Behind a window the first keep_first keys stay visible: tiles over [0, sink_end) come first, then the
+    // tiles of the window.  Both are aligned to absolute positions, and keys between the two are seen by no
+    // query of this block (k_begin is not above any query's window).
+    const int sink_end = window > 0 ? min(min(keep_first, k_begin), k_end) : 0;
+    const int n_sink = (sink_end + KT - 1) / KT;
+    const int n_tiles = n_sink + (k_end > k_begin ? (k_end - k_begin + KT - 1) / KT : 0);
 
-    for (int kt = k_begin; kt < k_end; kt += KT) {
+    for (int ti = 0; ti < n_tiles; ++ti) {
+        const int kt = ti < n_sink ? ti * KT : k_begin + (ti - n_sink) * KT;
+        const int k_lim = ti < n_sink ? sink_end : k_end;
         __syncthreads();                         // the tile before is consumed (first time: Qs, Mx written)
         if (tid < KT) {
             const int kj = kt + tid;
             int s = -1;
-            if (kj < k_end) {
+            if (kj < k_lim) {
                 const int page = table[kj / page_size];
                 if (page >= 0) s = page * page_size + kj % page_size;
             }
@@ -175,7 +205,7 @@ attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const 
             AT v = from_float<AT>(0.f);
             if (s >= 0) {
                 const int page = s / page_size, off = s - page * page_size;
-                v = v_cache[(((int64_t)page * G + g) * page_size + off) * dv + c];
+                v = v_cache[(((int64_t)page * G + g) * page_size + off) * vrs + c];
             }
             KV[idx] = v;
         }
@@ -190,7 +220,8 @@ attn_mix_kernel(const AT* __restrict__ q, const AT* __restrict__ k_cache, const 
                 s = S1[r * SP + j];
             }
             const int kj = kt + j, pos = p_lo + i;
-            const bool vis = i < nq && kj <= pos && (window == 0 || kj > pos - window) && slot_of[j] >= 0;
+            const bool vis = i < nq && kj <= pos && (window == 0 || kj > pos - window || kj < keep_first) &&
+                             slot_of[j] >= 0;
             S2[r * SP + j] = vis ? s : -INFINITY;
         }
         __syncthreads();
@@ -307,15 +338,22 @@ extern "C" {
 
 int mi_rope_store(const float* qkv, const int* positions, const float* inv_freq, const int* slot_mapping,
                   void* q_out, void* k_cache, void* v_cache, int adtype, int T, int nh, int nkv, int dk, int dv,
-                  int rot_dim, int page_size, cudaStream_t stream) {
+                  int rot_dim, int page_size, const float* q_gain, const float* k_gain, float eps,
+                  cudaStream_t stream) {
     if (T <= 0) return kOk;
+    if ((q_gain == nullptr) != (k_gain == nullptr)) {
+        set_last_error("rope_store: the gains of the query norm and of the key norm come together");
+        return kBadShape;
+    }
     if (rot_dim < 0 || rot_dim > dk || rot_dim % 2 || (rot_dim > 0 && !inv_freq)) {
         set_last_error("rope_store: %d rotary dimensions of a head of %d", rot_dim, dk);
         return kBadShape;
     }
     MI_DISPATCH_1(adtype, AT,
-        launch_dependent(rope_store_kernel<AT>, dim3(T), dim3(256), sizeof(float) * (rot_dim > 0 ? rot_dim : 1), stream, qkv, positions, inv_freq,
-                         slot_mapping, (AT*)q_out, (AT*)k_cache, (AT*)v_cache, nh, nkv, dk, dv, rot_dim, page_size));
+        launch_dependent(rope_store_kernel<AT>, dim3(T), dim3(256),
+                         sizeof(float) * ((rot_dim > 0 ? rot_dim : 1) + nh + nkv), stream, qkv, positions, inv_freq,
+                         slot_mapping, (AT*)q_out, (AT*)k_cache, (AT*)v_cache, nh, nkv, dk, dv, rot_dim, page_size,
+                         q_gain, k_gain, eps));
     return finish_launch("rope_store");
 }
 
@@ -328,8 +366,12 @@ int mi_attn_mix_supported(int H, int G, int dk, int dv, int esize) {
 int mi_attn_mix(const void* q, const void* k_cache, const void* v_cache, int adtype, const float* mix,
                 const int* block_table, const int* q_start, const int* kv_len, void* out, int B, int max_q_len,
                 int H, int G, int dk, int dv, int page_size, int max_pages, int window, float scale, float cap,
-                cudaStream_t stream) {
+                int keep_first, int vrs, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return kOk;
+    if (keep_first < 0 || vrs < dv) {
+        set_last_error("mixed-head attention: %d kept first keys, value rows of %d every %d elements", keep_first, dv, vrs);
+        return kBadShape;
+    }
     if (H < 1 || G < 1 || H % G || dk < 1 || dv < 1 || dv > 256) {
         set_last_error("mixed-head attention: heads %d, key/value heads %d, key size %d, value size %d (at most 256)",
                        H, G, dk, dv);
@@ -349,7 +391,8 @@ int mi_attn_mix(const void* q, const void* k_cache, const void* v_cache, int adt
         cudaFuncSetAttribute(attn_mix_kernel<AT, CPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem); \
         launch_dependent(attn_mix_kernel<AT, CPL>, grid, dim3(256), p.smem, stream, (const AT*)q,            \
                          (const AT*)k_cache, (const AT*)v_cache, mix, block_table, q_start, kv_len, (AT*)out, \
-                         H, G, dk, dv, page_size, max_pages, window, scale, cap, p.QT, p.KT, p.rpw);          \
+                         H, G, dk, dv, page_size, max_pages, window, scale, cap, p.QT, p.KT, p.rpw,          \
+                         keep_first, vrs);                                                                    \
     })
     if (cpl <= 1) MI_MIX_LAUNCH(1);
     else if (cpl <= 2) MI_MIX_LAUNCH(2);

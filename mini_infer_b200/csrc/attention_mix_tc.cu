@@ -10,6 +10,8 @@
 //      second buffer
 //   4. running softmax in the layout of the A fragments (a row's maximum and sum live in a quad of lanes),
 //      O_h += P_h V_g with V fragments fetched by ldmatrix.trans from the row-major tile
+// Behind a window the first keep_first keys of a request stay visible; a value row may be the leading part of
+// a longer row (`vrs` elements from one token's values to the next one's).
 // Steps of one token per request are split over the keys (blocks of 64 keys write a partial maximum, sum
 // and unnormalised output; a merge kernel finishes), since one block per request cannot pull a window of
 // keys from memory fast enough.
@@ -55,7 +57,7 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ block_table, const int* __restrict__ q_start,
                    const int* __restrict__ kv_len, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int H, int G, int dk, int page_size, int max_pages, int window,
-                   float scale, float cap, int splits, int hgroups) {
+                   float scale, float cap, int splits, int hgroups, int keep_first, int vrs) {
     constexpr int DV = NT * 8;
     constexpr int SP = KT + 1;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -111,21 +113,33 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     if (window > 0) k_begin = max(0, p_lo - window + 1);
     k_begin = (k_begin / KT) * KT;
     int k_end = min(kvl, p_hi + 1);
+    // behind a window the first keep_first keys stay visible: tiles over [0, sink_end) come before the
+    // window's tiles (see attention_mix.cu); of a split step the last block takes them
+    int sink_end = window > 0 ? min(min(keep_first, k_begin), k_end) : 0;
     if (splits > 1) {
-        k_begin += split * kTcSplitKeys;
-        k_end = min(k_end, k_begin + kTcSplitKeys);
+        if (keep_first > 0 && split == splits - 1) {
+            k_begin = k_end;                     // the kept first keys alone
+        } else {
+            sink_end = 0;
+            k_begin += split * kTcSplitKeys;
+            k_end = min(k_end, k_begin + kTcSplitKeys);
+        }
     }
+    const int n_sink = (sink_end + KT - 1) / KT;
+    const int n_tiles = n_sink + (k_end > k_begin ? (k_end - k_begin + KT - 1) / KT : 0);
+    auto tile_start = [&](int ti) { return ti < n_sink ? ti * KT : k_begin + (ti - n_sink) * KT; };
+    auto tile_limit = [&](int ti) { return ti < n_sink ? sink_end : k_end; };
     const int* table = block_table + (size_t)b * max_pages;
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
     // Keys and values travel a step ahead of their use (cp.async): the values of a tile are asked for before its
     // scores are formed, the keys of the next tile as soon as the scores have left the key buffer.
     constexpr int vchunks = DV / 8;
-    auto find_slots = [&](int kt, int* slot_of) {
+    auto find_slots = [&](int ti, int* slot_of) {
         if (tid < KT) {
-            const int kj = kt + tid;
+            const int kj = tile_start(ti) + tid;
             int s = -1;
-            if (kj < k_end) {
+            if (kj < tile_limit(ti)) {
                 const int page = table[kj / page_size];
                 if (page >= 0) s = page * page_size + kj % page_size;
             }
@@ -152,25 +166,26 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             __nv_bfloat16* dst = Vb + ((size_t)g * KT + j) * dvp + c8 * 8;
             if (s >= 0) {
                 const int page = s / page_size, off = s - page * page_size;
-                tile_copy_16(dst, v_cache + (((size_t)page * G + g) * page_size + off) * DV + c8 * 8);
+                tile_copy_16(dst, v_cache + (((size_t)page * G + g) * page_size + off) * vrs + c8 * 8);
             } else {
                 *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
             }
         }
     };
-    if (k_begin < k_end) {
-        find_slots(k_begin, slots);
+    if (n_tiles > 0) {
+        find_slots(0, slots);
         __syncthreads();
         fetch_keys(slots);
     }
     tile_copy_commit();
     int which = 0;
-    for (int kt = k_begin; kt < k_end; kt += KT, which ^= 1) {
+    for (int ti = 0; ti < n_tiles; ++ti, which ^= 1) {
+        const int kt = tile_start(ti);
         const int* slot_of = slots + which * KT;
         __syncthreads();                         // the tile before has left the value buffer and its scores
         fetch_values(slot_of);
         tile_copy_commit();
-        if (kt + KT < k_end) find_slots(kt + KT, slots + (which ^ 1) * KT);
+        if (ti + 1 < n_tiles) find_slots(ti + 1, slots + (which ^ 1) * KT);
         tile_copy_wait_but_one();                // this tile's keys
         __syncthreads();
         // ---- scores of all heads ----
@@ -210,12 +225,13 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         }
         __syncthreads();
         // ---- the next tile's keys set off; mix and mask ----
-        if (kt + KT < k_end) fetch_keys(slots + (which ^ 1) * KT);
+        if (ti + 1 < n_tiles) fetch_keys(slots + (which ^ 1) * KT);
         tile_copy_commit();
         for (int e = tid; e < kTcQ * KT; e += 256) {
             const int i = e / KT, j = e - i * KT;
             const int kj = kt + j, pos = p_lo + i;
-            const bool vis = i < nq && kj <= pos && (window == 0 || kj > pos - window) && slot_of[j] >= 0;
+            const bool vis = i < nq && kj <= pos && (window == 0 || kj > pos - window || kj < keep_first) &&
+                             slot_of[j] >= 0;
             if (!vis) {
                 for (int h = h_lo; h < h_hi; ++h) S2[((h - h_lo) * kTcQ + i) * SP + j] = -INFINITY;
             } else if (!mix) {
@@ -405,8 +421,13 @@ int mi_attn_mix_tc_splits(int span) { return (span + kTcSplitKeys - 1) / kTcSpli
 int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, const float* mix, const int* block_table,
                    const int* q_start, const int* kv_len, void* out, float* part_o, float* part_ml, int B,
                    int max_q_len, int H, int G, int dk, int dv, int page_size, int max_pages, int window,
-                   float scale, float cap, int splits, cudaStream_t stream) {
+                   float scale, float cap, int splits, int keep_first, int vrs, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0) return kOk;
+    if (keep_first < 0 || vrs < dv || vrs % 8) {
+        set_last_error("mixed-head attention (tensor cores): %d kept first keys, value rows of %d every %d elements",
+                       keep_first, dv, vrs);
+        return kBadShape;
+    }
     const TcPlan plan = tc_plan(H, G, dk, dv);
     const int kt = plan.kt;
     if (!kt) {
@@ -426,7 +447,7 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
         launch_dependent(attn_mix_tc_kernel<HPW, NT, KT>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)q, \
                          (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, mix, block_table, q_start, \
                          kv_len, (__nv_bfloat16*)out, part_o, part_ml, H, G, dk, page_size, max_pages, window,  \
-                         scale, cap, splits, hgroups);                                                          \
+                         scale, cap, splits, hgroups, keep_first, vrs);                                         \
     } while (0)
 #define MI_TC_KT(HPW, NT) do { if (kt == 32) MI_TC_LAUNCH(HPW, NT, 32); else MI_TC_LAUNCH(HPW, NT, 16); } while (0)
     if (dv == 128) {

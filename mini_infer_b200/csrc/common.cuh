@@ -40,6 +40,14 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// A gated unit with bounded halves: g = min(gate, limit), u = clamp(up, -limit, limit),
+// g * logistic(slope * g) * (u + 1).
+__device__ __forceinline__ float clamped_glu_f(float gate, float up, float limit, float slope) {
+    const float g = fminf(gate, limit);
+    const float u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -16,7 +16,9 @@ constexpr int DF_BM = 64, DF_BN = 64, DF_BK = 16;
 template <bool VEC>
 __global__ void __launch_bounds__(256)
 dense_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int T, int N,
-                 int K) {
+                 int K, int lda, int ldc, int64_t sA, int64_t sW, int64_t sC) {
+    // blockIdx.z: one of several independent products (a head, say) whose operands lie sA, sW, sC apart
+    A += blockIdx.z * sA; W += blockIdx.z * sW; C += blockIdx.z * sC;
     __shared__ float As[DF_BK][DF_BM + 4];
     __shared__ float Ws[DF_BK][DF_BN + 4];
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -31,7 +33,7 @@ dense_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float
             const int r = tid >> 2, c = (tid & 3) * 4;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), w = a;
             if (k0 + c < K) {
-                if (row0 + r < T) a = __ldg(reinterpret_cast<const float4*>(A + (int64_t)(row0 + r) * K + k0 + c));
+                if (row0 + r < T) a = __ldg(reinterpret_cast<const float4*>(A + (int64_t)(row0 + r) * lda + k0 + c));
                 if (n0 + r < N) w = __ldg(reinterpret_cast<const float4*>(W + (int64_t)(n0 + r) * K + k0 + c));
             }
             As[c][r] = a.x; As[c + 1][r] = a.y; As[c + 2][r] = a.z; As[c + 3][r] = a.w;
@@ -40,7 +42,7 @@ dense_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float
             for (int idx = tid; idx < DF_BM * DF_BK; idx += 256) {
                 const int r = idx / DF_BK, c = idx % DF_BK;
                 const bool kin = k0 + c < K;
-                As[c][r] = (kin && row0 + r < T) ? A[(int64_t)(row0 + r) * K + k0 + c] : 0.f;
+                As[c][r] = (kin && row0 + r < T) ? A[(int64_t)(row0 + r) * lda + k0 + c] : 0.f;
                 Ws[c][r] = (kin && n0 + r < N) ? W[(int64_t)(n0 + r) * K + k0 + c] : 0.f;
             }
         }
@@ -64,7 +66,7 @@ dense_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < N) C[(int64_t)r * N + n] = acc[i][j];
+            if (n < N) C[(int64_t)r * ldc + n] = acc[i][j];
         }
     }
 }
@@ -79,7 +81,28 @@ extern "C" int mi_dense_f32(const float* A, const float* W, float* C, int T, int
     if (tiles_y > 65535) { set_last_error("dense product (float32): %d rows exceed the grid limit", T); return kBadShape; }
     const dim3 grid((N + DF_BN - 1) / DF_BN, (unsigned)tiles_y);
     const bool vec = (K % 4 == 0) && (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) == 0);
-    if (vec) dense_f32_kernel<true><<<grid, 256, 0, stream>>>(A, W, C, T, N, K);
-    else dense_f32_kernel<false><<<grid, 256, 0, stream>>>(A, W, C, T, N, K);
+    if (vec) dense_f32_kernel<true><<<grid, 256, 0, stream>>>(A, W, C, T, N, K, K, N, 0, 0, 0);
+    else dense_f32_kernel<false><<<grid, 256, 0, stream>>>(A, W, C, T, N, K, K, N, 0, 0, 0);
     return finish_launch("dense_f32");
+}
+
+// `batch` products at once: C_b[T, N] = A_b[T, K] . W_b[N, K]^T with rows of A and C `lda` and `ldc` floats
+// apart and the operands of product b at A + b * sA, W + b * sW (rows K apart), C + b * sC: the heads of a
+// row of activations, each with a matrix of its own.  The same chain of additions per element as above.
+extern "C" int mi_dense_f32_batched(const float* A, const float* W, float* C, int T, int N, int K, int lda, int ldc,
+                                    int batch, int64_t sA, int64_t sW, int64_t sC, cudaStream_t stream) {
+    using namespace mi;
+    if (T <= 0 || N <= 0 || batch <= 0) return kOk;
+    if (K <= 0 || lda < K || ldc < N || batch > 65535) {
+        set_last_error("batched dense product (float32): inner size %d, rows %d and %d apart, %d products", K, lda, ldc, batch);
+        return kBadShape;
+    }
+    const int64_t tiles_y = ((int64_t)T + DF_BM - 1) / DF_BM;
+    if (tiles_y > 65535) { set_last_error("batched dense product (float32): %d rows exceed the grid limit", T); return kBadShape; }
+    const dim3 grid((N + DF_BN - 1) / DF_BN, (unsigned)tiles_y, batch);
+    const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (sA % 4 == 0) && (sW % 4 == 0) &&
+                     (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) == 0);
+    if (vec) dense_f32_kernel<true><<<grid, 256, 0, stream>>>(A, W, C, T, N, K, lda, ldc, sA, sW, sC);
+    else dense_f32_kernel<false><<<grid, 256, 0, stream>>>(A, W, C, T, N, K, lda, ldc, sA, sW, sC);
+    return finish_launch("dense_f32_batched");
 }

@@ -337,12 +337,17 @@ __device__ __forceinline__ void router_select_token(const float* __restrict__ z,
                                                     int* __restrict__ topk_idx, float* __restrict__ topk_w,
                                                     float* __restrict__ gate, float* __restrict__ probs_out,
                                                     float* p, int* idx_copy, int t, int E, int K,
-                                                    int norm_topk) {
+                                                    int norm_topk, const float* __restrict__ bias = nullptr) {
     const int lane = threadIdx.x & 31;
     const int ncols = E + (has_gate ? 1 : 0);
     const float* zr = z + (int64_t)t * ncols;
     float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) { const float v = __ldcg(zr + e); p[e] = v; mx = fmaxf(mx, v); }
+    for (int e = lane; e < E; e += 32) {
+        float v = __ldcg(zr + e);
+        if (bias) v += bias[e];                  // a bias per expert joins the logit before anything is chosen
+        p[e] = v;
+        mx = fmaxf(mx, v);
+    }
     const float gl = (has_gate && lane == 0) ? __ldcg(zr + E) : 0.f;
     router_select_loaded(mx, gl, has_gate, topk_idx, topk_w, gate, probs_out, p, idx_copy, t, E, K, norm_topk);
 }
@@ -363,13 +368,13 @@ __device__ __forceinline__ void router_select_logits(const float* zs, int has_ga
 __global__ void __launch_bounds__(256)
 moe_router_select_kernel(const float* __restrict__ z, int has_gate, int* __restrict__ topk_idx,
                          float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
-                         int T, int E, int K, int norm_topk) {
+                         int T, int E, int K, int norm_topk, const float* __restrict__ bias) {
     extern __shared__ float smem[];  // [8][E]
     const int warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 8 + warp;
     if (t >= T) return;
     router_select_token(z, has_gate, topk_idx, topk_w, gate, probs_out, smem + warp * E, nullptr, t, E, K,
-                        norm_topk);
+                        norm_topk, bias);
 }
 
 // ---------------------------------------------------------------------------
@@ -436,7 +441,7 @@ moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, cons
                        float* __restrict__ z, unsigned* __restrict__ tickets, int* __restrict__ topk_idx,
                        float* __restrict__ topk_w, float* __restrict__ gate, float* __restrict__ probs_out,
                        int* __restrict__ offsets, int* __restrict__ sorted_token, int* __restrict__ inv_perm,
-                       int T, int H, int E, int K, int norm_topk) {
+                       int T, int H, int E, int K, int norm_topk, const float* __restrict__ bias) {
     extern __shared__ int route_sh[];  // select: [TOK][E] floats; then permute: [E+1] + [T*K] ints
     __shared__ bool last;
     const int grp = blockIdx.y, t0 = grp * TOK;
@@ -451,7 +456,7 @@ moe_route_small_kernel(const AT* __restrict__ x, const WT* __restrict__ wr, cons
     const int warp = threadIdx.x >> 5;
     if (warp < TOK && t0 + warp < T)
         router_select_token(z, wsg ? 1 : 0, topk_idx, topk_w, gate, probs_out,
-                            reinterpret_cast<float*>(route_sh) + warp * E, nullptr, t0 + warp, E, K, norm_topk);
+                            reinterpret_cast<float*>(route_sh) + warp * E, nullptr, t0 + warp, E, K, norm_topk, bias);
     if (!offsets) return;
     __threadfence();
     __syncthreads();
@@ -769,7 +774,7 @@ extern "C" {
 // `z_scratch` holds T * (E + 1) floats (router logits and the shared gate's logit).
 int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, int wdtype, float* z_scratch,
                   int* topk_idx, float* topk_w, float* gate, float* probs_out, int T, int H, int E, int K,
-                  int norm_topk, cudaStream_t stream) {
+                  int norm_topk, const float* bias, cudaStream_t stream) {
     if (T <= 0) return kOk;
     if (K < 1 || K > 32 || K > E) {
         set_last_error("router: experts per token %d must lie in [1, min(32, %d)]", K, E);
@@ -799,7 +804,7 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
             moe_router_logits_small_kernel<AT, WT><<<sgrid, 256, 0, stream>>>(
                 (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, T, H, E));
         moe_router_select_kernel<<<(T + 7) / 8, 256, smem_p, stream>>>(z_scratch, wsg ? 1 : 0, topk_idx, topk_w,
-                                                                        gate, probs_out, T, E, K, norm_topk);
+                                                                        gate, probs_out, T, E, K, norm_topk, bias);
         return finish_launch("moe_router", 2);
     }
     if (adtype == kBF16 && wdtype == kBF16 && H % 32 == 0 &&
@@ -809,7 +814,7 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
             moe_router_logits_mma_kernel<<<mgrid, 32 * RM_WARPS, 0, stream>>>(
                 (const __nv_bfloat16*)x, (const __nv_bfloat16*)wr, (const __nv_bfloat16*)wsg, z_scratch, T, H, E);
             moe_router_select_kernel<<<(T + 7) / 8, 256, smem_p, stream>>>(z_scratch, wsg ? 1 : 0, topk_idx, topk_w,
-                                                                            gate, probs_out, T, E, K, norm_topk);
+                                                                            gate, probs_out, T, E, K, norm_topk, bias);
             return finish_launch("moe_router", 2);
         }
     }
@@ -822,7 +827,7 @@ int mi_moe_router(const void* x, int adtype, const void* wr, const void* wsg, in
         moe_router_logits_kernel<AT, WT><<<grid, 32 * RT_ROWS, smem_x, stream>>>(
             (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, T, H, E, rows_per_block));
     moe_router_select_kernel<<<(T + 7) / 8, 256, smem_p, stream>>>(z_scratch, wsg ? 1 : 0, topk_idx, topk_w, gate,
-                                                                    probs_out, T, E, K, norm_topk);
+                                                                    probs_out, T, E, K, norm_topk, bias);
     return finish_launch("moe_router", 2);
 }
 
@@ -834,7 +839,7 @@ int mi_moe_route_small_max_tokens() { return 128; }
 int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* wsg, int wdtype, float* z_scratch,
                        unsigned* tickets, int* topk_idx, float* topk_w, float* gate, float* probs_out,
                        int* offsets, int* sorted_token, int* inv_perm, int T, int H, int E, int K, int norm_topk,
-                       cudaStream_t stream) {
+                       const float* bias, cudaStream_t stream) {
     if (T <= 0) return kOk;
     if (T > mi_moe_route_small_max_tokens()) {
         set_last_error("router (decode): %d tokens, takes at most %d", T, mi_moe_route_small_max_tokens());
@@ -860,7 +865,7 @@ int mi_moe_route_small(const void* x, int adtype, const void* wr, const void* ws
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
         moe_route_small_kernel<AT, WT, TOK><<<grid, 256, smem, stream>>>(                                      \
             (const AT*)x, (const WT*)wr, (const WT*)wsg, z_scratch, tickets, topk_idx, topk_w, gate, probs_out, \
-            offsets, sorted_token, inv_perm, T, H, E, K, norm_topk);                                           \
+            offsets, sorted_token, inv_perm, T, H, E, K, norm_topk, bias);                                     \
     } while (0)
     if (tok == 1) {
         MI_DISPATCH_2(adtype, AT, wdtype, WT, MI_ROUTE_LAUNCH(AT, WT, 1));

@@ -4,6 +4,8 @@
 //                         outputs that differ by a scalar gain only: the two norms of a block whose mixer
 //                         and feed-forward read the same residual, when each norm's weight is one number
 //   geglu_tanh            out = gelu_tanh(gate) * up, gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+//   clamped_glu           out = g s(a g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit),
+//                         s the logistic function: a gated unit whose two halves are bounded before they meet
 //   concat_cast           out[t] = [hidden[t] + a[t] + b[t] | other[t]] in the activation type: the input
 //                         of a projection that reads the residual beside a second stream
 //   rows_plus_vec         hidden[t] = y[t] + vec: a projection's result becomes the residual, plus one row
@@ -66,6 +68,19 @@ __global__ void geglu_tanh_kernel(const AT* __restrict__ gu, AT* __restrict__ ou
         const float g = to_float(gu[t * 2 * I + i]);
         const float u = to_float(gu[t * 2 * I + I + i]);
         out[idx] = from_float<AT>(gelu_tanh_f(g) * u);
+    }
+}
+
+// gate and up halves of float rows [T, 2 I] -> [T, I] in the activation type
+template <typename AT>
+__global__ void clamped_glu_kernel(const float* __restrict__ gu, AT* __restrict__ out, int64_t total, int I,
+                                   float limit, float slope) {
+    wait_for_earlier_kernels();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        out[idx] = from_float<AT>(clamped_glu_f(gu[t * 2 * I + i], gu[t * 2 * I + I + i], limit, slope));
     }
 }
 
@@ -152,6 +167,18 @@ int mi_geglu_tanh(const void* gu, void* out, int adtype, int64_t T, int I, cudaS
         launch_dependent(geglu_tanh_kernel<AT>, dim3((int)blocks), dim3(256), 0, stream, (const AT*)gu, (AT*)out,
                          total, I));
     return finish_launch("geglu_tanh");
+}
+
+int mi_clamped_glu(const float* gu, void* out, int adtype, int64_t T, int I, float limit, float slope,
+                   cudaStream_t stream) {
+    const int64_t total = T * I;
+    if (total <= 0) return kOk;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    MI_DISPATCH_1(adtype, AT,
+        launch_dependent(clamped_glu_kernel<AT>, dim3((int)blocks), dim3(256), 0, stream, gu, (AT*)out, total, I,
+                         limit, slope));
+    return finish_launch("clamped_glu");
 }
 
 int mi_concat_cast(const float* hidden, const float* a, const float* b, const float* other, void* out, int adtype,

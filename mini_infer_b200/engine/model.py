@@ -10,6 +10,7 @@ which norms and projects every row; here only the rows whose logits are wanted.
 
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -86,6 +87,13 @@ class Model:
                     if not isinstance(src, PagedCacheNeed) or src.geometry() != need.geometry():
                         raise ValueError(f"schedule[{pos}] reads the cache of schedule[{e.cache_from}], "
                                          f"whose geometry differs")
+                    # the owner keeps a token's entry for as long as any of its readers looks back
+                    if (need.window, need.keep_first) != (src.window, src.keep_first):
+                        window = 0 if 0 in (need.window, src.window) else max(need.window, src.window)
+                        widened = dataclasses.replace(src, window=window,
+                                                      keep_first=max(need.keep_first, src.keep_first))
+                        needs[e.cache_from][role] = widened
+                        paged[:] = [(o, widened if o == (e.cache_from, role) else n) for o, n in paged]
                     continue
                 if isinstance(need, PagedCacheNeed):
                     paged.append(((pos, role), need))

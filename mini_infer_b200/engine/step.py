@@ -111,7 +111,7 @@ class ModelRunner:
         for g in groups:
             n = max(1, int(num_pages * float(g.need.pages_fraction)))
             if g.window > 0:
-                per_request = -(-(g.window + self.max_tokens) // self.page_size) + 2
+                per_request = -(-(g.window + self.max_tokens) // self.page_size) + 2 + -(-g.keep_first // self.page_size)
                 n = min(n, max_requests * min(per_request, -(-self.max_context // self.page_size)))
             pages.append(n)
         self.cache = CacheManager(groups, pages, page_size, max_requests)

@@ -447,13 +447,15 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
 
 def moe_router(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
-               norm_topk: bool, want_probs: bool = False
+               norm_topk: bool, want_probs: bool = False, bias: Optional[torch.Tensor] = None
                ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
-    """Router of one layer.  Returns ``(idx [T,K] int32, w [T,K] f32, gate [T] f32 | None, probs | None)``."""
+    """Router of one layer.  Returns ``(idx [T,K] int32, w [T,K] f32, gate [T] f32 | None, probs | None)``.
+    ``bias`` (float32 ``[E]``) is added to the logits before the softmax and the choice."""
     _chk(x, "moe_router x")
     T, H = x.shape
     _chk(router_w, "moe_router weight", None, (None, H))
     E = router_w.shape[0]
+    _chk(bias, "moe_router bias", F32, (E,))
     if shared_gate_w is not None:
         _chk(shared_gate_w, "moe_router shared gate", router_w.dtype)
         if shared_gate_w.numel() != H:
@@ -466,7 +468,7 @@ def moe_router(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[
     z = torch.empty(T, E + 1, dtype=F32, device=dev)
     check(library().mi_moe_router(_ptr(x), _code(x, "moe_router x"), _ptr(router_w), _ptr(shared_gate_w),
                                   _code(router_w, "moe_router weight"), _ptr(z), _ptr(idx), _ptr(w), _ptr(gate),
-                                  _ptr(probs), T, H, E, int(top_k), int(bool(norm_topk)), _stream()),
+                                  _ptr(probs), T, H, E, int(top_k), int(bool(norm_topk)), _ptr(bias), _stream()),
           "moe_router")
     return idx, w, gate, probs
 
@@ -495,7 +497,8 @@ def route_small_max_tokens() -> int:
 
 
 def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Optional[torch.Tensor], top_k: int,
-                    norm_topk: bool, ticket: torch.Tensor, want_probs: bool = False, permute: bool = True):
+                    norm_topk: bool, ticket: torch.Tensor, want_probs: bool = False, permute: bool = True,
+                    bias: Optional[torch.Tensor] = None):
     """:func:`moe_router` and (with ``permute``) :func:`moe_permute` of a step of a few tokens in
     one launch.
 
@@ -513,6 +516,7 @@ def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Opti
         if shared_gate_w.numel() != H:
             raise ValueError("moe_route_small: the shared-expert gate must have hidden_size entries")
     _chk(ticket, "moe_route_small ticket", I32)
+    _chk(bias, "moe_route_small bias", F32, (E,))
     if ticket.numel() < 1 + T:
         raise ValueError(f"moe_route_small: {ticket.numel()} ticket counters for {T} tokens (1 + T wanted)")
     dev = x.device
@@ -529,8 +533,8 @@ def moe_route_small(x: torch.Tensor, router_w: torch.Tensor, shared_gate_w: Opti
     check(library().mi_moe_route_small(
         _ptr(x), _code(x, "moe_route_small x"), _ptr(router_w), _ptr(shared_gate_w),
         _code(router_w, "moe_route_small weight"), _ptr(z), _ptr(ticket), _ptr(idx), _ptr(w), _ptr(gate), _ptr(probs),
-        _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T, H, E, int(top_k), int(bool(norm_topk)), _stream()),
-        "moe_route_small")
+        _ptr(offsets), _ptr(sorted_token), _ptr(inv_perm), T, H, E, int(top_k), int(bool(norm_topk)), _ptr(bias),
+        _stream()), "moe_route_small")
     return idx, w, gate, probs, offsets, sorted_token, inv_perm
 
 
@@ -1086,10 +1090,16 @@ def gated_group_rmsnorm(y: torch.Tensor, gate: torch.Tensor, gate_col: int, weig
 
 def rope_store(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rot_dim: int,
                slot_mapping: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, nh: int, nkv: int,
-               dk: int, dv: int, page_size: int, out_dtype: torch.dtype) -> torch.Tensor:
+               dk: int, dv: int, page_size: int, out_dtype: torch.dtype,
+               q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
+               eps: float = 0.0) -> torch.Tensor:
     """Rotary encoding of the first ``rot_dim`` dimensions of the query and key heads of float32 rows
     ``[nh*dk | nkv*dk | nkv*dv]``, cache write of keys ``[pages, nkv, page_size, dk]`` and values
-    ``[pages, nkv, page_size, dv]`` (slot -1: not written).  Returns ``q [T, nh, dk]`` in ``out_dtype``."""
+    ``[pages, nkv, page_size, dv]`` (slot -1: not written).  With ``q_gain`` and ``k_gain`` (float32
+    ``[dk]``) every query and key head is first divided by its root mean square (``eps`` inside the root) and
+    multiplied by the gain.  Returns ``q [T, nh, dk]`` in ``out_dtype``."""
+    _chk(q_gain, "rope_store q_gain", F32, (dk,))
+    _chk(k_gain, "rope_store k_gain", F32, (dk,))
     _chk(qkv, "rope_store qkv", F32)
     T = qkv.shape[0]
     _chk(qkv, "rope_store qkv", F32, (T, (nh + nkv) * dk + nkv * dv))
@@ -1105,7 +1115,8 @@ def rope_store(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[to
         _dbg_range(slot_mapping, -1, k_cache.shape[0] * page_size, "rope_store slot_mapping")
     check(library().mi_rope_store(_ptr(qkv), _ptr(positions), _ptr(inv_freq), _ptr(slot_mapping), _ptr(q),
                                   _ptr(k_cache), _ptr(v_cache), _code(q, "rope_store q"), T, nh, nkv, dk, dv,
-                                  int(rot_dim), page_size, _stream()), "rope_store")
+                                  int(rot_dim), page_size, _ptr(q_gain), _ptr(k_gain), float(eps), _stream()),
+          "rope_store")
     return q
 
 
@@ -1115,16 +1126,23 @@ def attention_mix_supported(nh: int, nkv: int, dk: int, dv: int, dtype: torch.dt
 
 def attention_mix(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, mix: Optional[torch.Tensor],
                   block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int,
-                  window: int, scale: float, softcap: float) -> torch.Tensor:
+                  window: int, scale: float, softcap: float, keep_first: int = 0,
+                  value_dim: int = 0) -> torch.Tensor:
     """Attention of a ragged batch over the paged cache with ``score <- softcap * tanh(score / softcap)``
     (``softcap`` 0: none) and then ``score_h <- sum_g mix[h, g] score_g`` (``mix`` None: none) before the
-    softmax over the visible keys.  Returns ``[T, nh, dv]``."""
+    softmax over the visible keys: key ``j`` is visible from position ``p`` iff ``j <= p`` and (``window`` is
+    0 or ``j > p - window`` or ``j < keep_first``).  With ``value_dim`` a token's value is the first
+    ``value_dim`` numbers of its row of ``v_cache`` (which may be the key cache itself).
+    Returns ``[T, nh, dv]``."""
     _chk(q, "attention_mix q")
     T, nh, dk = q.shape
     _chk(k_cache, "attention_mix k_cache", q.dtype)
     _, nkv, page_size, dk2 = k_cache.shape
     _chk(v_cache, "attention_mix v_cache", q.dtype, (k_cache.shape[0], nkv, page_size, None))
-    dv = v_cache.shape[3]
+    vrs = v_cache.shape[3]
+    dv = int(value_dim) or vrs
+    if dv > vrs:
+        raise ValueError(f"attention_mix: values of {dv} in rows of {vrs}")
     if dk2 != dk:
         raise ValueError(f"attention_mix: key size of q ({dk}) and of the cache ({dk2}) differ")
     _chk(mix, "attention_mix mix", F32, (nh, nh))
@@ -1138,8 +1156,8 @@ def attention_mix(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                    int(max_q_len))
     check(library().mi_attn_mix(_ptr(q), _ptr(k_cache), _ptr(v_cache), _code(q, "attention_mix q"), _ptr(mix),
                                 _ptr(block_table), _ptr(q_start), _ptr(kv_len), _ptr(out), B, int(max_q_len), nh, nkv,
-                                dk, dv, page_size, max_pages, int(window), float(scale), float(softcap), _stream()),
-          "attention_mix")
+                                dk, dv, page_size, max_pages, int(window), float(scale), float(softcap),
+                                int(keep_first), vrs, _stream()), "attention_mix")
     return out
 
 
@@ -1148,24 +1166,29 @@ def attention_mix_tc_supported(nh: int, nkv: int, dk: int, dv: int) -> bool:
     return bool(library().mi_attn_mix_tc_supported(nh, nkv, dk, dv))
 
 
-def attention_mix_tc_splits(span: int) -> int:
-    """Blocks over the keys that a step of single tokens is cut into when a query sees up to ``span`` keys."""
-    return int(library().mi_attn_mix_tc_splits(int(span)))
+def attention_mix_tc_splits(span: int, keep_first: int = 0) -> int:
+    """Blocks over the keys that a step of single tokens is cut into when a query sees up to ``span`` keys
+    of its window (one block more for kept first keys)."""
+    return int(library().mi_attn_mix_tc_splits(int(span))) + (1 if keep_first > 0 else 0)
 
 
 def attention_mix_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, mix: Optional[torch.Tensor],
                      block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor, max_q_len: int,
                      window: int, scale: float, softcap: float, splits: int = 1,
-                     part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                     keep_first: int = 0, value_dim: int = 0) -> torch.Tensor:
     """:func:`attention_mix` on the tensor cores (bfloat16).  ``splits > 1`` (steps of one token per request
     only): the keys of a request are cut into ``splits`` blocks whose partial results go through the float32
-    scratch ``part_o`` (``B * splits * nh * dv``) and ``part_ml`` (``B * splits * nh * 2``)."""
+    scratch ``part_o`` (``B * splits * nh * dv``) and ``part_ml`` (``B * splits * nh * 2``); with
+    ``keep_first`` the last of the blocks takes the kept first keys, so ``splits`` counts one more
+    (:func:`attention_mix_tc_splits`)."""
     _chk(q, "attention_mix_tc q", BF16)
     T, nh, dk = q.shape
     _chk(k_cache, "attention_mix_tc k_cache", BF16, (None, None, None, dk))
     _, nkv, page_size, _ = k_cache.shape
     _chk(v_cache, "attention_mix_tc v_cache", BF16, (k_cache.shape[0], nkv, page_size, None))
-    dv = v_cache.shape[3]
+    vrs = v_cache.shape[3]
+    dv = int(value_dim) or vrs
     _chk(mix, "attention_mix_tc mix", F32, (nh, nh))
     _chk(block_table, "attention_mix_tc block_table", I32)
     B, max_pages = block_table.shape
@@ -1183,5 +1206,97 @@ def attention_mix_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     check(library().mi_attn_mix_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(mix), _ptr(block_table), _ptr(q_start),
                                    _ptr(kv_len), _ptr(out), _ptr(part_o), _ptr(part_ml), B, int(max_q_len), nh, nkv, dk,
                                    dv, page_size, max_pages, int(window), float(scale), float(softcap), int(splits),
-                                   _stream()), "attention_mix_tc")
+                                   int(keep_first), vrs, _stream()), "attention_mix_tc")
+    return out
+
+
+def clamped_glu(gu: torch.Tensor, limit: float, slope: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``g * logistic(slope * g) * (u + 1)`` with ``g = min(gate, limit)`` and ``u = clamp(up, -limit, limit)``
+    of float32 rows ``[T, 2 I]`` (gate half, then up half); returns ``[T, I]`` in ``out_dtype``."""
+    _chk(gu, "clamped_glu", F32)
+    T, I2 = gu.shape
+    if I2 % 2:
+        raise ValueError("clamped_glu: rows hold a gate half and an up half")
+    out = torch.empty(T, I2 // 2, dtype=out_dtype, device=gu.device)
+    check(library().mi_clamped_glu(_ptr(gu), _ptr(out), _code(out, "clamped_glu out"), T, I2 // 2, float(limit),
+                                   float(slope), _stream()), "clamped_glu")
+    return out
+
+
+def dense_f32_heads(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, x_col: int = 0,
+                    x_head_stride: Optional[int] = None, out_col: int = 0,
+                    out_head_stride: Optional[int] = None) -> torch.Tensor:
+    """A product per head in true float32: ``out[t, h] = w[h] @ x[t, h]`` with ``w [H, N, K]``.  ``x`` is
+    ``[T, *]`` float32 rows in which head ``h`` starts at column ``x_col + h * x_head_stride`` (default: heads
+    of ``K`` side by side); ``out`` likewise (default ``[T, H * N]``).  The same fixed chain of additions per
+    element as :func:`dense_f32`."""
+    _chk(x, "dense_f32_heads x", F32)
+    _chk(w, "dense_f32_heads w", F32)
+    H, N, K = w.shape
+    T = x.shape[0]
+    xs = K if x_head_stride is None else int(x_head_stride)
+    os_ = N if out_head_stride is None else int(out_head_stride)
+    lda = x.numel() // max(T, 1)
+    if out is None:
+        out = torch.empty(T, H * N, dtype=F32, device=x.device)
+    _chk(out, "dense_f32_heads out", F32)
+    ldc = out.numel() // max(T, 1)
+    if x_col + (H - 1) * xs + K > lda or out_col + (H - 1) * os_ + N > ldc:
+        raise ValueError("dense_f32_heads: the heads do not fit the rows")
+    check(library().mi_dense_f32_batched(x.data_ptr() + 4 * x_col, _ptr(w), out.data_ptr() + 4 * out_col, T, N, K,
+                                         lda, ldc, H, xs, N * K, os_, _stream()), "dense_f32_heads")
+    return out
+
+
+def latent_store(src: torch.Tensor, col0: int, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                 gain: torch.Tensor, eps: float, slot_mapping: torch.Tensor, cache: torch.Tensor, rank: int,
+                 rot_dim: int) -> None:
+    """The cached row of every token: columns ``col0 .. col0 + rank`` of the float32 rows ``src`` divided by
+    their root mean square (``eps`` inside the root) times ``gain``, then ``rot_dim`` columns rotated by
+    position in pairs of neighbours.  ``cache [pages, 1, page_size, rank + rot_dim]``; slot -1: not written."""
+    _chk(src, "latent_store src", F32)
+    T, ld = src.shape
+    _chk(positions, "latent_store positions", I32, (T,))
+    _chk(inv_freq, "latent_store inv_freq", F32, (rot_dim // 2,))
+    _chk(gain, "latent_store gain", F32, (rank,))
+    _chk(slot_mapping, "latent_store slot_mapping", I32, (T,))
+    _chk(cache, "latent_store cache", None, (None, 1, None, rank + rot_dim))
+    if DEBUG_BOUNDS:
+        _dbg_range(slot_mapping, -1, cache.shape[0] * cache.shape[2], "latent_store slot_mapping")
+    check(library().mi_latent_store(_ptr(src), ld, int(col0), _ptr(positions), _ptr(inv_freq), _ptr(gain), float(eps),
+                                    _ptr(slot_mapping), _ptr(cache), _code(cache, "latent_store cache"), T, int(rank),
+                                    int(rot_dim), _stream()), "latent_store")
+
+
+def latent_query(q: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor], heads: int, dim: int,
+                 rot_dim: int, rank: int, out_dtype: torch.dtype, want_plain: bool):
+    """Float32 rows of ``heads`` queries ``[dim unrotated | rot_dim rotated]``: returns ``(q_full, q_plain)``
+    where ``q_full [T, heads, rank + rot_dim]`` (``out_dtype``) has its last ``rot_dim`` columns filled with the
+    parts rotated by position (pairs of neighbours; the first ``rank`` are left for the folded queries) and
+    ``q_plain [T, heads, dim]`` holds the unrotated parts in ``out_dtype`` (None unless wanted)."""
+    _chk(q, "latent_query q", F32)
+    T = q.shape[0]
+    _chk(q, "latent_query q", F32, (T, heads * (dim + rot_dim)))
+    _chk(positions, "latent_query positions", I32, (T,))
+    _chk(inv_freq, "latent_query inv_freq", F32, (rot_dim // 2,))
+    q_full = torch.empty(T, heads, rank + rot_dim, dtype=out_dtype, device=q.device)
+    q_plain = torch.empty(T, heads, dim, dtype=out_dtype, device=q.device) if want_plain else None
+    check(library().mi_latent_query(_ptr(q), _ptr(positions), _ptr(inv_freq), _ptr(q_plain), _ptr(q_full),
+                                    _code(q_full, "latent_query out"), T, heads, dim, rot_dim, rank, _stream()),
+          "latent_query")
+    return q_full, q_plain
+
+
+def sigmoid_gate(a: torch.Tensor, head_major: bool, g: torch.Tensor, col0: int, heads: int, size: int) -> torch.Tensor:
+    """``out[t, h, :] = a[t, h, :] * logistic(g[t, col0 + h * size : ...])``; ``a`` is ``[T, heads, size]`` or,
+    with ``head_major``, ``[heads, T, size]``; ``g`` float32 rows.  Returns ``[T, heads * size]`` in ``a``'s type."""
+    _chk(a, "sigmoid_gate a")
+    _chk(g, "sigmoid_gate g", F32)
+    T = g.shape[0]
+    if a.numel() != T * heads * size:
+        raise ValueError("sigmoid_gate: sizes of the heads' outputs and of the gate differ")
+    out = torch.empty(T, heads * size, dtype=a.dtype, device=a.device)
+    a_head, a_tok = (T * size, size) if head_major else (size, heads * size)
+    check(library().mi_sigmoid_gate(_ptr(a), a_head, a_tok, _ptr(g), g.shape[1], int(col0), _ptr(out),
+                                    _code(a, "sigmoid_gate a"), T, heads, size, _stream()), "sigmoid_gate")
     return out

@@ -29,12 +29,12 @@ _SIGNATURES = {
     "mi_attn_tiled": [P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_decode": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P],
     "mi_attn_decode_split": [P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
-    "mi_moe_router": [P, I, P, P, I, P, P, P, P, P, I, I, I, I, I, P],
+    "mi_moe_router": [P, I, P, P, I, P, P, P, P, P, I, I, I, I, I, P, P],
     "mi_moe_permute": [P, P, P, P, P, I, I, I, P],
     "mi_grouped_gemm_plain": [P, I, P, P, I, P, P, I, I, I, I, I, I, P],
     "mi_sample_rows": [P, P, P, P, P, P, I, I, P],
     "mi_grouped_gemm_skinny": [P, P, P, P, P, I, I, I, I, P],
-    "mi_moe_route_small": [P, I, P, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "mi_moe_route_small": [P, I, P, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
     "mi_moe_norm_route_small": [P, P, P, I, F, P, I, P, P, I, P, P, P, P, I, I, I, I, I, P],
     "mi_grouped_gemm_skinny_pairs": [P, P, P, P, I, I, I, I, I, I, P],
     "mi_qkv_skinny": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
@@ -51,13 +51,18 @@ _SIGNATURES = {
     "mi_delta_scan": [P, I, P, I, P, I, P, P, P, L, P, P, P, P, I, I, I, I, I, I, F, P],
     "mi_ssd_scan": [P, I, P, I, P, P, P, P, L, P, P, P, I, I, I, I, I, P],
     "mi_gated_group_rmsnorm": [P, P, I, P, I, I, P, I, I, I, I, I, F, P],
-    "mi_rope_store": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
-    "mi_attn_mix": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P],
-    "mi_attn_mix_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, P],
+    "mi_rope_store": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, F, P],
+    "mi_attn_mix": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, P],
+    "mi_attn_mix_tc": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, I, I, I, P],
     "mi_add2_rmsnorm_scalar": [P, P, P, P, P, P, P, P, I, I, I, F, P],
     "mi_geglu_tanh": [P, P, I, L, I, P],
     "mi_concat_cast": [P, P, P, P, P, I, I, I, P],
     "mi_rows_plus_vec": [P, P, P, I, I, I, P],
+    "mi_clamped_glu": [P, P, I, L, I, F, F, P],
+    "mi_dense_f32_batched": [P, P, P, I, I, I, I, I, I, L, L, L, P],
+    "mi_latent_store": [P, I, I, P, P, P, F, P, P, I, I, I, I, P],
+    "mi_latent_query": [P, P, P, P, P, I, I, I, I, I, I, P],
+    "mi_sigmoid_gate": [P, L, L, P, I, I, P, I, I, I, I, P],
 }
 
 

@@ -1,6 +1,7 @@
 """Attention over the paged cache whose heads exchange their scores before the softmax.
 
-``score = (q . k) * scale``; ``score <- softcap * tanh(score / softcap)`` (if a cap is set); then every
+Optionally every query and key head is first brought to unit root mean square and given a gain per
+dimension.  ``score = (q . k) * scale``; ``score <- softcap * tanh(score / softcap)`` (if a cap is set); then every
 head's score of a (query, key) pair becomes a mix of all heads' scores of that pair,
 ``score_h <- sum_g talk[h, g] * score_g`` (if the layer has such a matrix); then the softmax over the keys a
 window lets through.  Query/key heads and value heads may differ in size.  One library product for q, k and
@@ -22,13 +23,17 @@ from .base import CacheBinding, KVNeed, Mixer, Runtime, StepContext, TensorDecl,
 
 class HeadMixAttention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim`` (queries and keys),
-    ``value_dim``, ``window`` (0 = all keys), ``scale``, ``softcap`` (0 = none), ``head_mix`` (the layer has a
-    ``[heads, heads]`` matrix that mixes the heads' scores), ``position`` (a ``PartSpec`` of category
-    ``position``), optional tensor names ``q``, ``k``, ``v``, ``o``, ``mix`` below the prefix.
+    ``value_dim``, ``window`` (0 = all keys), ``keep_first`` (behind a window the first so many keys of a
+    request stay visible, at their true positions; 0 = none), ``scale``, ``softcap`` (0 = none), ``head_mix``
+    (the layer has a ``[heads, heads]`` matrix that mixes the heads' scores), ``qk_norm`` (``{"eps": ...}``:
+    every query and key head is divided by its root mean square and multiplied by a gain per dimension that
+    the heads share, before the rotation), ``position`` (a ``PartSpec`` of category ``position``), optional
+    tensor names ``q``, ``k``, ``v``, ``o``, ``mix``, ``q_norm``, ``k_norm`` below the prefix.
 
     Tensors: ``<prefix>q [heads*head_dim, hidden]``, ``<prefix>k [kv_heads*head_dim, hidden]``,
     ``<prefix>v [kv_heads*value_dim, hidden]``, ``<prefix>o [hidden, heads*value_dim]``,
-    ``<prefix>talk [heads, heads]`` if ``head_mix``."""
+    ``<prefix>talk [heads, heads]`` if ``head_mix``, ``<prefix>q.norm``, ``<prefix>k.norm [head_dim]`` if
+    ``qk_norm``."""
 
     graph_safe = True
 
@@ -41,6 +46,8 @@ class HeadMixAttention(Mixer):
         self.dk = int(p["head_dim"])
         self.dv = int(p.get("value_dim", self.dk))
         self.window = int(p.get("window", 0))
+        self.keep_first = int(p.get("keep_first", 0) or 0) if self.window > 0 else 0
+        self.qk_norm = p.get("qk_norm")
         self.scale = float(p.get("scale", self.dk ** -0.5))
         self.softcap = float(p.get("softcap", 0.0) or 0.0)
         self.head_mix = bool(p.get("head_mix", False))
@@ -48,7 +55,8 @@ class HeadMixAttention(Mixer):
         self.position = part_class("position", pos.kind)(pos.params, prefix)
         if self.nkv < 1 or self.nh % self.nkv:
             raise ValueError(f"attention: {self.nh} heads are not a multiple of {self.nkv} key/value heads")
-        self.names = {k: prefix + p.get(k, d) for k, d in (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"), ("mix", "talk"))}
+        self.names = {k: prefix + p.get(k, d) for k, d in (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"), ("mix", "talk"),
+                                                            ("q_norm", "q.norm"), ("k_norm", "k.norm"))}
 
     def tensor_decls(self) -> List[TensorDecl]:
         n = self.names
@@ -56,6 +64,8 @@ class HeadMixAttention(Mixer):
                TensorDecl(n["v"], (self.nkv * self.dv, self.H))]
         if self.head_mix:
             out.append(TensorDecl(n["mix"], (self.nh, self.nh), "head_mix"))
+        if self.qk_norm is not None:
+            out += [TensorDecl(n["q_norm"], (self.dk,), "norm"), TensorDecl(n["k_norm"], (self.dk,), "norm")]
         out.append(TensorDecl(n["o"], (self.H, self.nh * self.dv)))
         return out
 
@@ -66,6 +76,13 @@ class HeadMixAttention(Mixer):
         self.w_o = m(tensors[n["o"]], dev)
         # the mix acts on float scores
         self.mix = tensors[n["mix"]].to(device=dev, dtype=torch.float32).contiguous() if self.head_mix else None
+        # the head norms are float arithmetic
+        self.q_gain = self.k_gain = None
+        self.qk_eps = 0.0
+        if self.qk_norm is not None:
+            self.q_gain = tensors[n["q_norm"]].to(device=dev, dtype=torch.float32).contiguous()
+            self.k_gain = tensors[n["k_norm"]].to(device=dev, dtype=torch.float32).contiguous()
+            self.qk_eps = float(self.qk_norm["eps"])
         self.inv_freq = self.position.table(dev)
         self.rot_dim = self.position.rot_dim if self.inv_freq is not None else 0
         if not F.attention_mix_supported(self.nh, self.nkv, self.dk, self.dv, rt.act):
@@ -79,14 +96,14 @@ class HeadMixAttention(Mixer):
         F.l2_prefetch(self.w_qkv)
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.dk, self.window, value_dim=self.dv)
+        return KVNeed(self.nkv, self.dk, self.window, value_dim=self.dv, keep_first=self.keep_first)
 
     def _span(self, max_kv_len: int) -> int:
         """Most keys a query can see."""
         return min(self.window, max_kv_len) if self.window > 0 else max_kv_len
 
     def scratch_need(self, max_requests: int, max_context: int) -> Dict[str, int]:
-        splits = F.attention_mix_tc_splits(self._span(max_context))
+        splits = F.attention_mix_tc_splits(self._span(max_context), self.keep_first)
         return {"attn_mix_part_o": max_requests * splits * self.nh * self.dv,
                 "attn_mix_part_ml": max_requests * splits * self.nh * 2}
 
@@ -95,20 +112,21 @@ class HeadMixAttention(Mixer):
         kc, vc = view.k[cache.layer_slot], view.v[cache.layer_slot]
         qkv = linear(x, self.w_qkv, torch.float32)
         q = F.rope_store(qkv, ctx.positions, self.inv_freq, self.rot_dim, view.slot_mapping, kc, vc, self.nh,
-                         self.nkv, self.dk, self.dv, view.page_size, self.rt.act)
+                         self.nkv, self.dk, self.dv, view.page_size, self.rt.act, self.q_gain, self.k_gain,
+                         self.qk_eps)
         if not self._tensor_cores:
             # float32: one kernel for every step, sums in an order that the cut of the step cannot change
             a = F.attention_mix(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
-                                self.window, self.scale, self.softcap)
+                                self.window, self.scale, self.softcap, self.keep_first)
         elif ctx.all_decode and "attn_mix_part_o" in ctx.scratch:
             # one token per request: a block per request could not pull a window of keys fast enough
-            splits = F.attention_mix_tc_splits(self._span(ctx.max_kv_len))
+            splits = F.attention_mix_tc_splits(self._span(ctx.max_kv_len), self.keep_first)
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, 1, self.window,
                                    self.scale, self.softcap, splits, ctx.scratch["attn_mix_part_o"],
-                                   ctx.scratch["attn_mix_part_ml"])
+                                   ctx.scratch["attn_mix_part_ml"], keep_first=self.keep_first)
         else:
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
-                                   self.window, self.scale, self.softcap)
+                                   self.window, self.scale, self.softcap, keep_first=self.keep_first)
         return linear(a.view(ctx.num_tokens, self.nh * self.dv), self.w_o, torch.float32)
 
 

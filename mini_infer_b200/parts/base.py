@@ -117,7 +117,7 @@ def configure_matmul_exactness() -> None:
 # what a part keeps between steps: see cache/needs.py
 # --------------------------------------------------------------------------- #
 
-from ..cache.needs import KVNeed, PagedCacheNeed, StateNeed  # noqa: E402  (re-exported for part authors)
+from ..cache.needs import KVNeed, LatentNeed, PagedCacheNeed, StateNeed  # noqa: E402  (re-exported for part authors)
 
 
 # --------------------------------------------------------------------------- #

@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..config.registry import register_part
+from ..config.registry import part_class, register_part
 from ..ops import functional as F
 from .tuning import TUNING
 from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, StepContext, TensorDecl, TensorSum,
@@ -38,23 +38,42 @@ class PreNormResidual(Block):
 
 class TokenEmbedding(Embedding):
     """params: ``vocab_size``, ``hidden_size``, optional ``tensor`` (the tensor's name below the prefix,
-    default ``weight``).  Tensor: ``<prefix>weight [V, H]``; no scaling
-    (src/model/transformer_model.cpp:561-565)."""
+    default ``weight``) and ``norm`` (a ``PartSpec`` of category ``norm`` whose ``rms_parameters()`` are
+    applied to every gathered row before it becomes the residual stream, which stays float32).
+    Tensor: ``<prefix>weight [V, H]``; no scaling (src/model/transformer_model.cpp:561-565)."""
 
     graph_safe = True
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.norm = None
+        spec = self.params.get("norm")
+        if spec is not None:
+            self.norm = part_class("norm", spec.kind)(spec.params, prefix)
 
     def _name(self) -> str:
         return self.prefix + self.params.get("tensor", "weight")
 
     def tensor_decls(self) -> List[TensorDecl]:
-        return [TensorDecl(self._name(), (self.params["vocab_size"], self.params["hidden_size"]))]
+        out = [TensorDecl(self._name(), (self.params["vocab_size"], self.params["hidden_size"]))]
+        if self.norm is not None:
+            out += self.norm.tensor_decls()
+        return out
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         self.weight = rt.precision.matrix(tensors[self._name()], rt.device)
+        if self.norm is not None:
+            self.norm.load(tensors, rt)
+            if self.norm.rms_parameters() is None:
+                raise ValueError("token_embedding: the norm of the embedding must be a plain RMS norm")
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
-        return F.embed_gather(token_ids, self.weight)
+        hidden = F.embed_gather(token_ids, self.weight)
+        if self.norm is None:
+            return hidden
+        weight, eps = self.norm.rms_parameters()
+        return F.add_rmsnorm(hidden, None, weight, eps, torch.float32)
 
 
 class LinearHead(LMHead):
@@ -89,7 +108,8 @@ class LinearHead(LMHead):
 class ParallelResidual(Block):
     """``x <- x + Mixer(Norm1(x)) + FFN(Norm2(x))``: both parts read the same residual and their outputs
     are added together.  params: ``feed_forward`` (default True; False: a layer of a mixer alone, with the
-    roles ``mixer_norm`` and ``mixer`` only).
+    roles ``mixer_norm`` and ``mixer`` only); ``shared_norm`` (default False; True: the layer has ONE norm,
+    ``mixer_norm``, and the feed-forward reads its output too: ``x <- x + Mixer(h) + FFN(h)``, ``h = Norm(x)``).
 
     The two outputs travel on as one pending sum (:class:`TensorSum`) and are added by whatever reads the
     residual next.  When both norms are :class:`~mini_infer_b200.parts.norm.ScalarRMSNorm` with the same
@@ -102,19 +122,23 @@ class ParallelResidual(Block):
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         self.has_ff = bool(self.params.get("feed_forward", True))
+        self.shared_norm = bool(self.params.get("shared_norm", False))
         self._side_stream = None
         self.roles = {"mixer_norm": "norm", "mixer": "mixer"}
         if self.has_ff:
-            self.roles.update({"feed_forward_norm": "norm", "feed_forward": "feed_forward"})
+            self.roles.update({"feed_forward": "feed_forward"} if self.shared_norm else
+                              {"feed_forward_norm": "norm", "feed_forward": "feed_forward"})
 
     def forward(self, layer: BuiltLayer, hidden: torch.Tensor, pending, ctx: StepContext, caches):
         n1 = layer.mixer_norm
         if not self.has_ff:
             x1 = apply_norm(n1, hidden, pending)
             return layer.mixer.forward(x1, ctx, caches.get("mixer"))
-        n2 = layer.feed_forward_norm
+        n2 = None if self.shared_norm else layer.feed_forward_norm
         pair = getattr(n1, "apply_pair", None)
-        if pair is not None and getattr(n2, "scalar_gain", None) is not None and n2.eps == n1.eps:
+        if n2 is None:
+            x1 = x2 = apply_norm(n1, hidden, pending)       # one norm: both parts read its output
+        elif pair is not None and getattr(n2, "scalar_gain", None) is not None and n2.eps == n1.eps:
             x1, x2 = pair(hidden, pending, n2)
         else:
             x1 = apply_norm(n1, hidden, pending)

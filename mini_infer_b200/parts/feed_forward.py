@@ -19,6 +19,9 @@ from .base import FeedForward, Runtime, StepContext, TensorDecl, WeightedRowSum,
 from .tuning import TUNING
 
 
+SWISH_SLOPE = 1.702     # sigmoid(1.702 z) z approximates gelu(z)
+
+
 class SwiGLUMLP(FeedForward):
     """``(silu(x Wg^T) * (x Wu^T)) Wd^T``.  params: ``hidden_size``, ``intermediate_size``.
 
@@ -51,13 +54,17 @@ class SwiGLUMLP(FeedForward):
 
 class GatedMLP(FeedForward):
     """``(act(x Wg^T) * (x Wu^T)) Wd^T`` with a choice of ``act``.  params: ``hidden_size``,
-    ``intermediate_size``, ``activation`` (``silu`` | ``gelu_tanh``), optional ``gate``, ``up``, ``down``
-    (tensor names below the prefix; default ``gate_proj.weight`` and so on).
+    ``intermediate_size``, ``activation`` (``silu`` | ``gelu_tanh`` | ``clamped_swish``), optional ``gate``,
+    ``up``, ``down`` (tensor names below the prefix; default ``gate_proj.weight`` and so on).
+
+    ``clamped_swish`` (params ``limit`` and optionally ``slope``, default 1.702) bounds both halves before
+    they meet: with ``g = min(x Wg^T, limit)`` and ``u = clamp(x Wu^T, -limit, limit)`` the gated unit is
+    ``g * sigmoid(slope * g) * (u + 1)``, formed in float32 from the float32 products.
 
     Tensors: ``<prefix><gate>, <prefix><up> [I, H]``, ``<prefix><down> [H, I]``."""
 
     graph_safe = True
-    ACTIVATIONS = ("silu", "gelu_tanh")
+    ACTIVATIONS = ("silu", "gelu_tanh", "clamped_swish")
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -67,6 +74,10 @@ class GatedMLP(FeedForward):
         if self.activation not in self.ACTIVATIONS:
             raise ValueError(f"gated_mlp: activation '{self.activation}' is not one of {self.ACTIVATIONS}")
         self.names = [self.prefix + self.params.get(k, k + "_proj.weight") for k in ("gate", "up", "down")]
+        self.limit = float(self.params.get("limit", 0.0))
+        self.slope = float(self.params.get("slope", SWISH_SLOPE))
+        if self.activation == "clamped_swish" and not self.limit > 0:
+            raise ValueError("gated_mlp: 'clamped_swish' needs a positive 'limit'")
 
     def tensor_decls(self) -> List[TensorDecl]:
         g, u, d = self.names
@@ -85,6 +96,9 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         if self.activation == "silu":
             return linear(linear_swiglu(x, self.w_gate_up, self.rt.act), self.w_down, torch.float32)
+        if self.activation == "clamped_swish":
+            act = F.clamped_glu(linear(x, self.w_gate_up, torch.float32), self.limit, self.slope, self.rt.act)
+            return linear(act, self.w_down, torch.float32)
         return linear(F.geglu_tanh(linear(x, self.w_gate_up, self.rt.act)), self.w_down, torch.float32)
 
 
@@ -92,9 +106,15 @@ class SparseMoE(FeedForward):
     """Softmax router, top-k routed SwiGLU experts, optional sigmoid-gated shared expert.
 
     params: ``hidden_size``, ``num_experts``, ``top_k``, ``expert_intermediate_size``,
-    ``shared_intermediate_size`` (0 = no shared expert), ``norm_topk_prob``.
+    ``shared_intermediate_size`` (0 = no shared expert), ``norm_topk_prob`` (the chosen experts' weights are
+    renormalised to sum to one, which makes them the softmax over the chosen logits alone);
+    ``activation`` of the experts (``silu``, default, or ``clamped_swish`` with ``limit`` and optionally
+    ``slope``, as in :class:`GatedMLP`); ``router_bias`` (the router has a bias per expert that joins the
+    logits before the choice); optional tensor names below the prefix: ``router`` (default
+    ``gate.weight``), ``router_bias_name`` (default ``gate.bias``), ``expert`` (a format with ``{e}``,
+    default ``experts.{e}.``), ``gate``, ``up``, ``down`` (default ``gate_proj.weight`` and so on).
 
-    Tensors: ``<prefix>gate.weight [E, H]``;
+    Tensors: ``<prefix>gate.weight [E, H]`` (and ``gate.bias [E]``);
     ``<prefix>experts.{e}.{gate,up}_proj.weight [mI, H]``, ``.down_proj.weight [H, mI]``;
     ``<prefix>shared_expert.{gate,up,down}_proj.weight``, ``<prefix>shared_expert_gate.weight [1, H]``.
     """
@@ -114,6 +134,18 @@ class SparseMoE(FeedForward):
         self.norm_topk = bool(p.get("norm_topk_prob", False))
         if not 1 <= self.K <= min(self.E, 32):
             raise ValueError(f"moe: top_k {self.K} must lie in [1, min(32, num_experts={self.E})]")
+        self.activation = p.get("activation", "silu")
+        if self.activation not in ("silu", "clamped_swish"):
+            raise ValueError(f"moe: expert activation '{self.activation}' is not 'silu' or 'clamped_swish'")
+        self.limit = float(p.get("limit", 0.0))
+        self.slope = float(p.get("slope", SWISH_SLOPE))
+        if self.activation == "clamped_swish" and not self.limit > 0:
+            raise ValueError("moe: 'clamped_swish' needs a positive 'limit'")
+        self.has_router_bias = bool(p.get("router_bias", False))
+        self._router_name = self.prefix + p.get("router", "gate.weight")
+        self._router_bias_name = self.prefix + p.get("router_bias_name", "gate.bias")
+        self._expert_format = p.get("expert", "experts.{e}.")
+        self._proj_names = tuple(p.get(k, k + "_proj.weight") for k in ("gate", "up", "down"))
         self.last_routing = None
         self.keep_routing = False
         self._side_stream = None
@@ -132,12 +164,15 @@ class SparseMoE(FeedForward):
 
     def tensor_decls(self) -> List[TensorDecl]:
         p = self.prefix
-        out = [TensorDecl(p + "gate.weight", (self.E, self.H))]
+        out = [TensorDecl(self._router_name, (self.E, self.H))]
+        if self.has_router_bias:
+            out.append(TensorDecl(self._router_bias_name, (self.E,), "bias"))
+        gn, un, dn = self._proj_names
         for e in range(self.E):
-            q = f"{p}experts.{e}."
-            out += [TensorDecl(q + "gate_proj.weight", (self.mI, self.H)),
-                    TensorDecl(q + "up_proj.weight", (self.mI, self.H)),
-                    TensorDecl(q + "down_proj.weight", (self.H, self.mI))]
+            q = p + self._expert_format.format(e=e)
+            out += [TensorDecl(q + gn, (self.mI, self.H)),
+                    TensorDecl(q + un, (self.mI, self.H)),
+                    TensorDecl(q + dn, (self.H, self.mI))]
         if self.sI > 0:
             q = p + "shared_expert."
             out += [TensorDecl(q + "gate_proj.weight", (self.sI, self.H)),
@@ -150,14 +185,18 @@ class SparseMoE(FeedForward):
         self.rt = rt
         m, dev, p = rt.precision.matrix, rt.device, self.prefix
         # router and shared gate feed float32 dot products only
-        self.w_router = rt.precision.small(tensors[p + "gate.weight"], dev)
+        self.w_router = rt.precision.small(tensors[self._router_name], dev)
+        # the bias joins float32 logits
+        self.b_router = (tensors[self._router_bias_name].to(device=dev, dtype=torch.float32).contiguous()
+                         if self.has_router_bias else None)
         self.w_gate_up = torch.empty(self.E, 2 * self.mI, self.H, dtype=rt.act, device=dev)
         self.w_down = torch.empty(self.E, self.H, self.mI, dtype=rt.act, device=dev)
+        gn, un, dn = self._proj_names
         for e in range(self.E):
-            q = f"{p}experts.{e}."
-            self.w_gate_up[e, :self.mI].copy_(tensors[q + "gate_proj.weight"])
-            self.w_gate_up[e, self.mI:].copy_(tensors[q + "up_proj.weight"])
-            self.w_down[e].copy_(tensors[q + "down_proj.weight"])
+            q = p + self._expert_format.format(e=e)
+            self.w_gate_up[e, :self.mI].copy_(tensors[q + gn])
+            self.w_gate_up[e, self.mI:].copy_(tensors[q + un])
+            self.w_down[e].copy_(tensors[q + dn])
         self.w_shared_gate = None
         if self.sI > 0:
             q = p + "shared_expert."
@@ -218,7 +257,8 @@ class SparseMoE(FeedForward):
         if ctx.prefetch is not None and self.sI > 0:
             # the routing that comes first hardly touches memory: the shared expert's weights arrive beside it
             ctx.prefetch((self.w_shared_gate_up, self.w_shared_down))
-        if (rms is not None and T <= TUNING.shared_expert_fork_after_routing_max_tokens and self._by_pair(T)
+        if (rms is not None and self.b_router is None
+                and T <= TUNING.shared_expert_fork_after_routing_max_tokens and self._by_pair(T)
                 and F.norm_route_small_takes(self.H, self.E, self.w_shared_gate is not None, self.w_router.dtype)
                 and (delta is None or isinstance(delta, torch.Tensor))):
             x, idx, w, gate, probs = F.moe_norm_route_small(
@@ -226,6 +266,14 @@ class SparseMoE(FeedForward):
                 self.norm_topk, want_probs=self.keep_routing)
             return self._run(x, ctx, (idx, w, gate, probs))
         return super().forward_from_residual(hidden, delta, norm, ctx)
+
+    def _gated(self, product) -> torch.Tensor:
+        """The experts' gated units: ``product(True)`` forms ``silu(gate) * up`` in the product's own
+        epilogue; for another activation ``product(False)`` gives the float32 halves and a row-wise kernel
+        joins them."""
+        if self.activation == "silu":
+            return product(True)
+        return F.clamped_glu(product(False), self.limit, self.slope, self.rt.act)
 
     def _few_rows_per_expert(self, T: int) -> bool:
         """Whether a step of T tokens takes the decode-sized expert products (every used expert's weights
@@ -242,8 +290,9 @@ class SparseMoE(FeedForward):
         return T * self.K <= rows * self.E
 
     def _by_pair(self, T: int) -> bool:
-        """... and without a permutation (result rows indexed by (token, slot) pair)."""
-        return T <= self._pairs_max and self._few_rows_per_expert(T)
+        """... and without a permutation (result rows indexed by (token, slot) pair).  (The pair-indexed
+        product forms its gated units in its own epilogue, which knows ``silu`` only.)"""
+        return self.activation == "silu" and T <= self._pairs_max and self._few_rows_per_expert(T)
 
     def _run(self, x: torch.Tensor, ctx: StepContext, routed) -> WeightedRowSum:
         T = x.shape[0]
@@ -261,10 +310,10 @@ class SparseMoE(FeedForward):
             else:
                 idx, w, gate, probs, _, _, _ = F.moe_route_small(
                     x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
-                    want_probs=self.keep_routing, permute=False)
+                    want_probs=self.keep_routing, permute=False, bias=self.b_router)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
-            act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True)
+            act = self._gated(lambda pair: F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, pair))
             y = F.grouped_gemm_skinny_pairs(act, idx, self.w_down, False)
             if ctx.prefetch is not None:
                 # while the experts' rows are summed and normalised, the next layer's first weights arrive
@@ -278,24 +327,25 @@ class SparseMoE(FeedForward):
                     and self.rt.act == torch.bfloat16:
                 idx, w, gate, probs, offsets, sorted_token, inv_perm = F.moe_route_small(
                     x, self.w_router, self.w_shared_gate, self.K, self.norm_topk, self._route_ticket,
-                    want_probs=self.keep_routing)
+                    want_probs=self.keep_routing, bias=self.b_router)
             else:
                 idx, w, gate, probs = F.moe_router(x, self.w_router, self.w_shared_gate, self.K, self.norm_topk,
-                                                   want_probs=self.keep_routing)
+                                                   want_probs=self.keep_routing, bias=self.b_router)
                 offsets, sorted_token, inv_perm = F.moe_permute(idx, self.E)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
             if self._few_rows_per_expert(T):
                 # a few rows per expert: bound by reading each used expert once
-                act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True)
+                act = self._gated(lambda pair: F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, pair))
                 y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)
             elif self._tc:
                 # many rows per expert: tensor-core tiles over the rows gathered into expert order
                 xs = F.gather_rows(x, sorted_token)
-                act = F.grouped_gemm_tc(xs, self.w_gate_up, offsets, True)
+                act = self._gated(lambda pair: F.grouped_gemm_tc(xs, self.w_gate_up, offsets, pair))
                 y = F.grouped_gemm_tc(act, self.w_down, offsets, False)
             else:
-                act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act)
+                act = self._gated(lambda pair: F.grouped_gemm_plain(
+                    x, sorted_token, self.w_gate_up, offsets, n, pair, self.rt.act if pair else torch.float32))
                 y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
         if self.keep_routing:
             self.last_routing = (idx, w, probs)

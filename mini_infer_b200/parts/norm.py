@@ -16,18 +16,28 @@ from .base import Deferred, Norm, Runtime, TensorDecl, WeightedRowSum, split_sum
 
 
 class RMSNorm(Norm):
-    """params: ``size``, ``eps``.  Tensor: ``<prefix>weight [size]``."""
+    """params: ``size``, ``eps``, optional ``tensor`` (the tensor's name below the prefix, default ``weight``)
+    and ``one_plus`` (the checkpoint holds the gain's offset from one: ``y = x * rsqrt(mean(x^2) + eps) *
+    (1 + w)``; the sum is formed once, in float32, when the weights are loaded).
+    Tensor: ``<prefix><tensor> [size]``."""
 
     graph_safe = True
     accepts_deferred = True
 
+    def _name(self) -> str:
+        return self.prefix + self.params.get("tensor", "weight")
+
     def tensor_decls(self) -> List[TensorDecl]:
-        return [TensorDecl(self.prefix + "weight", (self.params["size"],), "norm")]
+        role = "norm_offset" if self.params.get("one_plus") else "norm"
+        return [TensorDecl(self._name(), (self.params["size"],), role)]
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         self.eps = float(self.params["eps"])
-        self.weight = rt.precision.small(tensors[self.prefix + "weight"], rt.device)
+        if self.params.get("one_plus"):
+            self.weight = (tensors[self._name()].to(device=rt.device, dtype=torch.float32) + 1.0).contiguous()
+        else:
+            self.weight = rt.precision.small(tensors[self._name()], rt.device)
 
     def rms_parameters(self):
         return self.weight, self.eps
