@@ -34,8 +34,9 @@ def _sparse_parts(runner):
     """{layer index: sparse feed-forward part} for layers that route."""
     out = {}
     for i, layer in enumerate(runner.model.layers):
-        if hasattr(layer.feed_forward, "keep_routing"):
-            out[i] = layer.feed_forward
+        part = layer.parts.get("feed_forward")           # a layer may have none
+        if hasattr(part, "keep_routing"):
+            out[i] = part
     return out
 
 

@@ -181,31 +181,33 @@ def gated_ff(h, w_gate, w_up, w_down, limit: float, rnd: Callable = same):
     return rnd(clamped_glu(h @ w_gate.T, h @ w_up.T, limit)) @ w_down.T
 
 
-def routed_ff(h, w, p: str, mlp: dict, rnd: Callable = same, chosen: Optional[list] = None):
+def routed_ff(h, w, p: str, mlp: dict, rnd: Callable = same, chosen: Optional[list] = None, forced=None):
     """The ``top`` experts with the largest router logits (weight times input plus bias); their weights are
-    the softmax over the chosen logits alone."""
+    the softmax over the chosen logits alone.  ``chosen`` receives ``(indices, logits)``; ``forced``
+    (``[T, top]``) replaces the choice (the weights are then the softmax over the forced experts' logits)."""
     E, K = mlp["router"]["experts"], mlp["router"]["top"]
     limit = mlp["expert"]["limit"]
     z = h.to(torch.float64) @ w[p + "router"].to(torch.float64).T + w[p + "router.b"].to(torch.float64)
-    top = torch.topk(z, K, dim=-1)
+    picked = torch.topk(z, K, dim=-1).indices if forced is None else forced
     if chosen is not None:
-        chosen.append(top.indices)
-    gate = torch.softmax(top.values, dim=-1).to(h.dtype)
+        chosen.append((picked, z))
+    gate = torch.softmax(z.gather(1, picked), dim=-1).to(h.dtype)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for slot in range(K):
-            e = int(top.indices[t, slot])
+            e = int(picked[t, slot])
             q = f"{p}e{e}."
             out[t] += gate[t, slot] * gated_ff(h[t:t + 1], w[q + "gate"], w[q + "up"], w[q + "down"], limit, rnd)[0]
     return out
 
 
-def feed_forward(h, w, p: str, mlp: Optional[dict], rnd: Callable = same, chosen: Optional[list] = None):
+def feed_forward(h, w, p: str, mlp: Optional[dict], rnd: Callable = same, chosen: Optional[list] = None,
+                 forced=None):
     if mlp is None:
         return torch.zeros_like(h)
     if mlp["kind"] == "dense":
         return gated_ff(h, w[p + "gate"], w[p + "up"], w[p + "down"], mlp["limit"], rnd)
-    return routed_ff(h, w, p, mlp, rnd, chosen)
+    return routed_ff(h, w, p, mlp, rnd, chosen, forced)
 
 
 # --------------------------------------------------------------------------- #
@@ -213,9 +215,11 @@ def feed_forward(h, w, p: str, mlp: Optional[dict], rnd: Callable = same, chosen
 # --------------------------------------------------------------------------- #
 
 def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
-            rnd: Callable = same, layers_out: Optional[list] = None, chosen: Optional[list] = None):
+            rnd: Callable = same, layers_out: Optional[list] = None, chosen: Optional[dict] = None,
+            forced: Optional[dict] = None):
     """Logits ``[T, vocab]`` of a whole sequence.  ``layers_out`` receives the residual stream after every
-    layer; ``chosen`` the experts picked by every routed layer."""
+    layer; ``chosen[layer]`` the ``(experts, router logits)`` of every routed layer; ``forced[layer]``
+    (``[T, top]``) overrides a routed layer's choice."""
     w = {k: v.to(dtype) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
     x = w["embed"][torch.tensor(tokens, dtype=torch.long)]
@@ -235,8 +239,20 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
             y = latent_attention_mixer(h, w, p + "mix.", m, eps, kept[src], rnd)
         else:
             raise ValueError(f"layer {i}: unknown type {layer['type']!r}")
-        x = x + (y + feed_forward(h, w, p + "mlp.", layer.get("mlp"), rnd, chosen))
+        rec = [] if chosen is not None else None
+        x = x + (y + feed_forward(h, w, p + "mlp.", layer.get("mlp"), rnd, rec,
+                                  None if forced is None else forced.get(i)))
+        if rec:
+            chosen[i] = rec[0]
         if layers_out is not None:
             layers_out.append(x.clone())
     x = rnd(norm_one_plus(x, w["final.norm"], eps))
     return x @ w["head"].T
+
+
+def greedy(config: dict, weights, prompt: List[int], n: int, dtype=torch.float64) -> List[int]:
+    """``n`` tokens, each the arg-max of the logits at the last position of all tokens so far."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(torch.argmax(forward(config, weights, toks, dtype)[-1])))
+    return toks[len(prompt):]
