@@ -567,12 +567,20 @@ def _twin_kernel_work(size, window, T, B, ctx, decode, layers):
 
 
 def run_vizalix(args):
-    """``--vizalix``: prefill and decode throughput of the Vizalix design at sizes that resemble a real
-    model's layers (random weights), beside the closest built-in model (an all-dense Qwen2-MoE with the same
-    width, heads, window, feed-forward width and as many layers as Vizalix has layer runs), with the device
-    time of every kernel of one step of each and, for the design's own kernels, the share of the roofline
-    (the slower of algorithmic bytes over the measured copy bandwidth and operations over the measured bf16
-    product rate).  Prints one JSON line; the default workload of this file is not touched."""
+    return _run_design(args, "vizalix", args.vizalix, args.vizalix_window,
+                       lambda size, window, vocab: vizalix_config(size, window, vocab),
+                       lambda size, window, vocab: dense_twin_config(size, window, vocab, 10),
+                       _vizalix_kernel_work,
+                       lambda cfg, size, window, T, B, ctx, dec: _twin_kernel_work(size, window, T, B, ctx, dec, 10),
+                       "dense_twin")
+
+
+def _run_design(args, design, sizes, window, make_config, make_twin, design_work, twin_work, twin_name):
+    """A design beside the closest built-in model: prefill and decode throughput at sizes that resemble a real
+    model's layers (random weights), with the device time of every kernel of one step of each and, for the
+    kernels that the work functions name, the share of the roofline (the slower of algorithmic bytes over the
+    measured copy bandwidth and operations over the measured bf16 product rate).  Prints one JSON line; the
+    default workload of this file is not touched."""
     import torch
     from mini_infer_b200.engine.defaults import DEFAULT_PAGE_SIZE
     from mini_infer_b200.engine.loading import random_model
@@ -580,15 +588,14 @@ def run_vizalix(args):
 
     pk = peaks()
     T, B, ctx, page = args.prompt_len, args.batch, args.prompt_len, DEFAULT_PAGE_SIZE
-    vocab, window = 32000, args.vizalix_window
-    result = {"metric": "vizalix_vs_dense_twin", "prompt_len": T, "decode_batch": B, "decode_context": ctx,
+    vocab = 32000
+    result = {"metric": f"{design}_vs_{twin_name}", "prompt_len": T, "decode_batch": B, "decode_context": ctx,
               "window": window, "dtype": "bf16", "data": "synthetic", "peaks": pk, "sizes": {}}
     sampler = ClockSampler()
     sampler.start()
-    for size in [x for x in args.vizalix.split(",") if x]:
+    for size in [x for x in sizes.split(",") if x]:
         entry = {}
-        vz = vizalix_config(size, window, vocab)
-        for which, cfg in (("vizalix", vz), ("dense_twin", dense_twin_config(size, window, vocab, 10))):
+        for which, cfg in ((design, make_config(size, window, vocab)), (twin_name, make_twin(size, window, vocab))):
             model, rt = random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0")
             runner = ModelRunner(model, rt, page_size=page, num_pages=(B + 1) * (-(-(ctx + 512) // page)) + 8,
                                  max_requests=max(B, 2), max_tokens_per_step=max(T, B), max_context=ctx + 512,
@@ -648,8 +655,8 @@ def run_vizalix(args):
                             "prefill_kernels": pf_kernels, "decode_kernels": dc_kernels}
             if True:
                 for phase, table, dec in (("prefill", pf_kernels, False), ("decode", dc_kernels, True)):
-                    work = (_vizalix_kernel_work(cfg, T, B, ctx, dec) if which == "vizalix"
-                            else _twin_kernel_work(size, window, T, B, ctx, dec, 10))
+                    work = (design_work(cfg, T, B, ctx, dec) if which == design
+                            else twin_work(cfg, size, window, T, B, ctx, dec))
                     for name, (by, fl) in work.items():
                         if name in table:
                             floor_us = max(by / (pk["hbm_gbs"] * 1e9), fl / (pk["bf16_tflops"] * 1e12)) * 1e6
@@ -662,6 +669,104 @@ def run_vizalix(args):
     print(json.dumps(result))
     return 0
 
+
+
+# --------------------------------------------------------------------------- #
+# --nipapel: the Nipapel design beside the closest built-in model (Qwen2-MoE) at equal sizes
+# --------------------------------------------------------------------------- #
+NIPAPEL_SIZES = {   # width, heads, key/value heads, head size, latent size, rotated size, query latent, latent heads'
+                    # unrotated size and value size, dense feed-forward, experts, experts per token, expert width
+    "0.5b": (1024, 8, 2, 128, 128, 32, 384, 64, 64, 2816, 16, 2, 1024),
+    "a2.7b": (2048, 16, 4, 128, 128, 64, 768, 64, 64, 5632, 60, 4, 1408),
+}
+NIPAPEL_LAYERS = 6
+
+
+def nipapel_config(size, window, vocab):
+    W, H, G, d, c, r, qr, dl, el, ff, E, K, eff = NIPAPEL_SIZES[size]
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": E, "top": K}}
+    attn = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "mask": {"size": window, "keep_first": 4},
+            "rot": {"base": 500000.0, "dims": d // 2}, "scale": d ** -0.5}
+
+    def latent(kv_from=None):
+        m = {"heads": H, "dim": dl, "rot_dim": r, "vdim": el, "kv_rank": c, "q_rank": qr, "mask": {"size": window},
+             "rot": {"base": 10000.0, "dims": r}, "scale": (dl + r) ** -0.5}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return m
+    layers = [{"type": "attention", "mixer": attn, "mlp": dense},
+              {"type": "latent_attention", "mixer": latent(), "mlp": moe},
+              {"type": "latent_attention", "mixer": latent(1), "mlp": moe},
+              {"type": "attention", "mixer": attn, "mlp": moe},
+              {"type": "latent_attention", "mixer": latent(), "mlp": moe},
+              {"type": "latent_attention", "mixer": latent(4), "mlp": moe}]
+    return {"architecture": "Nipapel", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def moe_twin_config(size, window, vocab):
+    """The closest built-in model: Qwen2-MoE with the same width, heads, window, experts and expert width, a
+    dense first layer of the same feed-forward width, no shared expert, as many layers."""
+    W, H, G, d, c, r, qr, dl, el, ff, E, K, eff = NIPAPEL_SIZES[size]
+    return dict(A27B, vocab_size=vocab, hidden_size=W, intermediate_size=ff, num_hidden_layers=NIPAPEL_LAYERS,
+                num_attention_heads=H, num_key_value_heads=G, head_dim=d, num_experts=E, num_experts_per_tok=K,
+                moe_intermediate_size=eff, shared_expert_intermediate_size=0, mlp_only_layers=[0],
+                norm_topk_prob=True, use_sliding_window=True, sliding_window=window, max_window_layers=0,
+                max_position_embeddings=1 << 20)
+
+
+def _nipapel_kernel_work(cfg, T, B, ctx, decode):
+    """Algorithmic bytes and floating-point operations of the design's own kernels for one step over all layers
+    (prefill of T tokens of one request, or a decode step of B requests at context ctx)."""
+    rows = B if decode else T
+    out = {}
+
+    def add(name, by, fl):
+        a = out.setdefault(name, [0.0, 0.0])
+        a[0] += by
+        a[1] += fl
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        win = m["mask"]["size"]
+        keys = min(ctx, win) + m["mask"].get("keep_first", 0)
+        pairs = B * keys if decode else sum(min(t + 1, win) for t in range(T))
+        if L["type"] == "attention":
+            H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            by = (B * keys * G * (d + e) * 2 + B * H * (d + e) * 2) if decode else T * (H + G) * (d + e) * 2
+            add("attn_mix_tc_kernel", by, pairs * H * (2.0 * d + 2.0 * e))
+            add("rope_store_kernel", rows * (H * d + G * (d + e)) * 6, 0)
+        else:
+            H, d, r, e, c = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            by = (B * keys * (c + r) * 2 + B * H * (2 * c + r) * 2) if decode else T * (H * (2 * c + r) + c + r) * 2
+            add("attn_mix_tc_kernel", by, pairs * H * (2.0 * (c + r) + 2.0 * c))
+            if m.get("kv_from") is None:
+                add("latent_store_kernel", rows * (c + r) * 6, 0)
+            add("latent_query_kernel", rows * H * ((d + r) * 4 + (d + r) * 2), 0)
+            add("sigmoid_gate_kernel", rows * H * e * (2 + 4 + 2), 0)
+        if L["mlp"]["kind"] == "dense":
+            add("clamped_glu_kernel", rows * L["mlp"]["ff"] * (8 + 2), 0)
+    return out
+
+
+def _moe_twin_kernel_work(cfg, size, window, T, B, ctx, decode):
+    W, H, G, d = NIPAPEL_SIZES[size][:4]
+    ff = NIPAPEL_SIZES[size][9]
+    rows, layers = (B if decode else T), NIPAPEL_LAYERS
+    if decode:
+        keys = min(ctx, window)
+        pairs, by = B * keys, B * keys * G * 2 * d * 2 + B * H * 2 * d * 2
+        attn = "attn_decode_split_kernel"
+    else:
+        pairs = sum(min(t + 1, window) for t in range(T))
+        by, attn = T * (H + G) * 2 * d * 2, "pt::attn_prefill_tc_kernel"
+    return {attn: [layers * by, layers * pairs * H * 4.0 * d],
+            "swiglu_bf16x8_kernel": [rows * ff * 6, 0.0],
+            "qkv_post_rows_kernel": [layers * rows * (H + 2 * G) * d * 6, 0.0]}
+
+
+def run_nipapel(args):
+    return _run_design(args, "nipapel", args.nipapel, args.nipapel_window, nipapel_config, moe_twin_config,
+                       _nipapel_kernel_work, _moe_twin_kernel_work, "moe_twin")
 
 
 def run_reference(args):
@@ -797,6 +902,10 @@ def main():
                     help="instead of the default workload: the Vizalix design beside the closest built-in model at "
                          "these sizes (comma-separated, of " + ", ".join(VIZALIX_SIZES) + "), see run_vizalix")
     ap.add_argument("--vizalix-window", type=int, default=1024, help="attention window of the --vizalix models")
+    ap.add_argument("--nipapel", default="", metavar="SIZES",
+                    help="instead of the default workload: prefill and decode of the Nipapel design beside Qwen2-MoE at "
+                         "these sizes (comma-separated, of " + ", ".join(NIPAPEL_SIZES) + "), see run_nipapel")
+    ap.add_argument("--nipapel-window", type=int, default=1024, help="attention window of the --nipapel models")
     ap.add_argument("--reference-timeout", type=int, default=1500, help="seconds the reference's program may take")
     ap.add_argument("--reference-prefill-batch", type=int, default=1,
                     help="prompts the reference's scheduler prefills per iteration (its cuBLAS handles, one per "
@@ -816,6 +925,8 @@ def main():
         return run_serving(args)
     if args.vizalix:
         return run_vizalix(args)
+    if args.nipapel:
+        return run_nipapel(args)
     return run_ours(args)
 
 

@@ -48,6 +48,23 @@ __device__ __forceinline__ float clamped_glu_f(float gate, float up, float limit
     return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
 }
 
+// How the two halves of a gated unit meet in a product's epilogue: kind 0 silu(gate) * up, kind 1 the
+// bounded form above.
+struct GluForm { int kind; float limit; float slope; };
+__device__ __forceinline__ float glu_join(float gate, float up, GluForm f) {
+    return f.kind == 1 ? clamped_glu_f(gate, up, f.limit, f.slope) : gate / (1.0f + expf(-gate)) * up;
+}
+
+// the same with the hardware's exponential and division, for epilogues that round to bfloat16 anyway
+__device__ __forceinline__ float glu_join_fast(float gate, float up, GluForm f) {
+    if (f.kind == 1) {
+        const float g = fminf(gate, f.limit);
+        const float u = fminf(fmaxf(up, -f.limit), f.limit);
+        return __fdividef(g, 1.0f + __expf(-f.slope * g)) * (u + 1.0f);
+    }
+    return __fdividef(gate, 1.0f + __expf(-gate)) * up;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -691,7 +691,8 @@ moe_permute_expert_kernel(const int* __restrict__ topk_idx, int* __restrict__ of
 // reference for the tensor-core kernels):
 //   rows r of expert e (offsets[e] <= r < offsets[e+1]), a_r = A[gather ? gather[r] : r, :]
 //   mode 0: C[r, n] = a_r . W[e, n, :]
-//   mode 1: C[r, n] = silu(a_r . W[e, n, :]) * (a_r . W[e, Nout + n, :])      (W is [E, 2*Nout, Kd])
+//   mode 1: C[r, n] = glu(a_r . W[e, n, :], a_r . W[e, Nout + n, :])          (W is [E, 2*Nout, Kd]; glu as
+//           the launch's GluForm says: silu(gate) * up, or the bounded form of common.cuh)
 // Tiles of 32 rows x 32 columns; the k loop runs in steps of 32 in ascending
 // order whatever the number of rows, so a row's sum never depends on its neighbours.
 // ---------------------------------------------------------------------------
@@ -700,7 +701,7 @@ constexpr int GB = 32;
 template <typename AT, typename WT, typename CT, int MODE>
 __global__ void __launch_bounds__(256)
 grouped_gemm_plain_kernel(const AT* __restrict__ A, const int* __restrict__ gather, const WT* __restrict__ W,
-                          const int* __restrict__ offsets, CT* __restrict__ C, int E, int Nout, int Kd) {
+                          const int* __restrict__ offsets, CT* __restrict__ C, int E, int Nout, int Kd, GluForm glu) {
     __shared__ float As[GB][GB + 1];
     __shared__ float Ws[GB][GB + 1];
     __shared__ float Us[MODE == 1 ? GB : 1][GB + 1];
@@ -758,7 +759,7 @@ grouped_gemm_plain_kernel(const AT* __restrict__ A, const int* __restrict__ gath
             const int r = ty * 4 + i;
             if (r < rows) {
                 float v = acc[i];
-                if (MODE == 1) v = v / (1.0f + expf(-v)) * acu[i];
+                if (MODE == 1) v = glu_join(v, acu[i], glu);
                 C[(int64_t)(row0 + r) * Nout + n] = from_float<CT>(v);
             }
         }
@@ -985,8 +986,9 @@ int mi_moe_permute(const int* topk_idx, int* offsets, int* sorted_token, int* in
 // cdtype: type of C (0 float, 1 bfloat16).  mode 1 = SwiGLU pair (W holds 2*Nout rows per expert).
 int mi_grouped_gemm_plain(const void* A, int adtype, const int* gather, const void* W, int wdtype,
                           const int* offsets, void* C, int cdtype, int n_rows, int E, int Nout, int Kd,
-                          int mode, cudaStream_t stream) {
+                          int mode, int glu_kind, float glu_limit, float glu_slope, cudaStream_t stream) {
     if (n_rows <= 0) return kOk;
+    const GluForm glu{glu_kind, glu_limit, glu_slope};
     const int max_tiles = (n_rows + GB - 1) / GB + E;
     if (max_tiles > 65535) {
         set_last_error("grouped product: %d row tiles exceed the grid limit", max_tiles);
@@ -996,7 +998,7 @@ int mi_grouped_gemm_plain(const void* A, int adtype, const int* gather, const vo
 #define MI_GG(MODE)                                                                                     \
     MI_DISPATCH_2(adtype, AT, wdtype, WT, MI_DISPATCH_1(cdtype, CT,                                     \
         grouped_gemm_plain_kernel<AT, WT, CT, MODE><<<grid, 256, 0, stream>>>(                          \
-            (const AT*)A, gather, (const WT*)W, offsets, (CT*)C, E, Nout, Kd)))
+            (const AT*)A, gather, (const WT*)W, offsets, (CT*)C, E, Nout, Kd, glu)))
     if (mode == 0) MI_GG(0); else MI_GG(1);
 #undef MI_GG
     return finish_launch("grouped_gemm_plain");

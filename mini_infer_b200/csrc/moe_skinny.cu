@@ -23,14 +23,15 @@ namespace mi {
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 
 // MODE 0: C[r, n] = a_r . W[e, n, :]                       (C float)
-// MODE 1: C[r, n] = silu(a_r . W[e, n, :]) * (a_r . W[e, Nout + n, :])   (C bfloat16)
+// MODE 1: C[r, n] = glu(a_r . W[e, n, :], a_r . W[e, Nout + n, :])   (C bfloat16; glu: silu(gate) * up, or the
+//         bounded form of common.cuh, as the launch's GluForm says)
 // Block = 4 warps x 16 features; grid = (ceil(Nout / 64), E).
 // Rows r < rows of this pass: source row src[r] (row0 + r without src), result row dst[r] (row0 + r
 // without dst).
 template <int MODE, int NT>
 __device__ __forceinline__ void skinny_pass(const __nv_bfloat16* __restrict__ A, const int* src, const int* dst,
                                             const __nv_bfloat16* __restrict__ We, void* __restrict__ C, int row0,
-                                            int rows, int f0, int Nout, int Kd) {
+                                            int rows, int f0, int Nout, int Kd, GluForm glu) {
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     // weight rows of this thread (clamped so that a partial feature tile never reads outside)
     const int fa = min(f0 + g, Nout - 1), fb = min(f0 + g + 8, Nout - 1);
@@ -89,7 +90,7 @@ __device__ __forceinline__ void skinny_pass(const __nv_bfloat16* __restrict__ A,
                 const int64_t o = (int64_t)(dst ? dst[r] : row0 + r) * Nout + f;
                 if (MODE == 1) {
                     const float gv = acc[j][0][i];
-                    reinterpret_cast<__nv_bfloat16*>(C)[o] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * acc[j][1][i]);
+                    reinterpret_cast<__nv_bfloat16*>(C)[o] = __float2bfloat16_rn(glu_join(gv, acc[j][1][i], glu));
                 } else {
                     reinterpret_cast<float*>(C)[o] = acc[j][0][i];
                 }
@@ -101,7 +102,7 @@ template <int MODE>
 __global__ void __launch_bounds__(128)
 grouped_gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ gather,
                            const __nv_bfloat16* __restrict__ W, const int* __restrict__ offsets,
-                           void* __restrict__ C, int Nout, int Kd) {
+                           void* __restrict__ C, int Nout, int Kd, GluForm glu) {
     const int e = blockIdx.y;
     const int b0 = offsets[e], cnt = offsets[e + 1] - b0;
     if (cnt <= 0) return;
@@ -110,11 +111,11 @@ grouped_gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const int* __res
     const int wrows = MODE == 1 ? 2 * Nout : Nout;
     const __nv_bfloat16* We = W + (int64_t)e * wrows * Kd;
     if (cnt <= 8) {
-        skinny_pass<MODE, 1>(A, gather ? gather + b0 : nullptr, nullptr, We, C, b0, cnt, f0, Nout, Kd);
+        skinny_pass<MODE, 1>(A, gather ? gather + b0 : nullptr, nullptr, We, C, b0, cnt, f0, Nout, Kd, glu);
     } else {
         for (int r0 = 0; r0 < cnt; r0 += 16)
             skinny_pass<MODE, 2>(A, gather ? gather + b0 + r0 : nullptr, nullptr, We, C, b0 + r0,
-                                 min(16, cnt - r0), f0, Nout, Kd);
+                                 min(16, cnt - r0), f0, Nout, Kd, glu);
     }
 }
 
@@ -129,7 +130,7 @@ template <int MODE>
 __global__ void __launch_bounds__(128)
 grouped_gemm_skinny_pairs_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ topk_idx,
                                  const __nv_bfloat16* __restrict__ W, void* __restrict__ C, int n_pairs, int K,
-                                 int src_is_token, int Nout, int Kd) {
+                                 int src_is_token, int Nout, int Kd, GluForm glu) {
     __shared__ int pair_sh[PAIR_MAX_TOKENS], from_sh[PAIR_MAX_TOKENS];
     __shared__ int cnt_sh;
     const int e = blockIdx.y;
@@ -157,10 +158,10 @@ grouped_gemm_skinny_pairs_kernel(const __nv_bfloat16* __restrict__ A, const int*
     const int wrows = MODE == 1 ? 2 * Nout : Nout;
     const __nv_bfloat16* We = W + (int64_t)e * wrows * Kd;
     if (cnt <= 8) {
-        skinny_pass<MODE, 1>(A, from_sh, pair_sh, We, C, 0, cnt, f0, Nout, Kd);
+        skinny_pass<MODE, 1>(A, from_sh, pair_sh, We, C, 0, cnt, f0, Nout, Kd, glu);
     } else {
         for (int r0 = 0; r0 < cnt; r0 += 16)
-            skinny_pass<MODE, 2>(A, from_sh + r0, pair_sh + r0, We, C, 0, min(16, cnt - r0), f0, Nout, Kd);
+            skinny_pass<MODE, 2>(A, from_sh + r0, pair_sh + r0, We, C, 0, min(16, cnt - r0), f0, Nout, Kd, glu);
     }
 }
 
@@ -174,7 +175,8 @@ grouped_gemm_skinny_pairs_kernel(const __nv_bfloat16* __restrict__ A, const int*
 template <int MODE, int NT, int WARPS = 8>
 __device__ __forceinline__ void splitk_tile(const __nv_bfloat16* __restrict__ A, const int* src, const int* dst,
                                             const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
-                                            void* __restrict__ C, int rows, int f0, int Nout, int Kd) {
+                                            void* __restrict__ C, int rows, int f0, int Nout, int Kd,
+                                            GluForm glu = GluForm{0, 0.f, 0.f}) {
     constexpr int H = MODE == 1 ? 2 : 1;
     __shared__ float red[WARPS][NT * H * 4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -247,7 +249,7 @@ __device__ __forceinline__ void splitk_tile(const __nv_bfloat16* __restrict__ A,
             const int64_t at = (int64_t)(dst ? dst[r] : r) * Nout + f;
             if (MODE == 1) {
                 if (bias) { s0 += bias[f]; s1 += bias[Nout + f]; }
-                reinterpret_cast<__nv_bfloat16*>(C)[at] = __float2bfloat16_rn(s0 / (1.0f + expf(-s0)) * s1);
+                reinterpret_cast<__nv_bfloat16*>(C)[at] = __float2bfloat16_rn(glu_join(s0, s1, glu));
             } else {
                 if (bias) s0 += bias[f];
                 reinterpret_cast<float*>(C)[at] = s0;
@@ -287,7 +289,7 @@ template <int MODE, bool COMPACT>
 __global__ void __launch_bounds__(256)
 grouped_gemm_skinny_pairs_splitk_kernel(const __nv_bfloat16* __restrict__ A, const int* __restrict__ topk_idx,
                                         const __nv_bfloat16* __restrict__ W, void* __restrict__ C, int n_pairs,
-                                        int K, int src_is_token, int Nout, int Kd) {
+                                        int K, int src_is_token, int Nout, int Kd, GluForm glu) {
     __shared__ int pair_sh[8], from_sh[8];
     __shared__ int cnt_sh, e_sh;
     wait_for_earlier_kernels();
@@ -331,7 +333,7 @@ grouped_gemm_skinny_pairs_splitk_kernel(const __nv_bfloat16* __restrict__ A, con
     const int cnt = cnt_sh, e = COMPACT ? e_sh : (int)blockIdx.y;
     if (cnt <= 0) return;
     const int wrows = MODE == 1 ? 2 * Nout : Nout;
-    splitk_tile<MODE, 1>(A, from_sh, pair_sh, W + (int64_t)e * wrows * Kd, nullptr, C, cnt, blockIdx.x * 16, Nout, Kd);
+    splitk_tile<MODE, 1>(A, from_sh, pair_sh, W + (int64_t)e * wrows * Kd, nullptr, C, cnt, blockIdx.x * 16, Nout, Kd, glu);
 }
 
 // Query/key/value projection of a step of a few tokens with its whole epilogue: bias, rotary
@@ -434,7 +436,9 @@ int mi_grouped_gemm_skinny_supported(int Kd) { return (Kd > 0 && Kd % 32 == 0) ?
 
 // A, W bfloat16; C bfloat16 for mode 1 (SwiGLU pair, W holds 2*Nout rows per expert), float for mode 0.
 int mi_grouped_gemm_skinny(const void* A, const int* gather, const void* W, const int* offsets, void* C,
-                           int E, int Nout, int Kd, int mode, cudaStream_t stream) {
+                           int E, int Nout, int Kd, int mode, int glu_kind, float glu_limit, float glu_slope,
+                           cudaStream_t stream) {
+    const GluForm glu{glu_kind, glu_limit, glu_slope};
     if (!mi_grouped_gemm_skinny_supported(Kd)) {
         set_last_error("grouped product (decode): inner size %d is not a multiple of 32", Kd);
         return kBadShape;
@@ -446,10 +450,10 @@ int mi_grouped_gemm_skinny(const void* A, const int* gather, const void* W, cons
     const dim3 grid((Nout + 63) / 64, E);
     if (mode == 1)
         grouped_gemm_skinny_kernel<1><<<grid, 128, 0, stream>>>(
-            (const __nv_bfloat16*)A, gather, (const __nv_bfloat16*)W, offsets, C, Nout, Kd);
+            (const __nv_bfloat16*)A, gather, (const __nv_bfloat16*)W, offsets, C, Nout, Kd, glu);
     else
         grouped_gemm_skinny_kernel<0><<<grid, 128, 0, stream>>>(
-            (const __nv_bfloat16*)A, gather, (const __nv_bfloat16*)W, offsets, C, Nout, Kd);
+            (const __nv_bfloat16*)A, gather, (const __nv_bfloat16*)W, offsets, C, Nout, Kd, glu);
     return finish_launch("grouped_gemm_skinny");
 }
 
@@ -463,7 +467,9 @@ int mi_grouped_gemm_skinny_pairs_split_inner_max_tokens() { return PAIR_SPLITK_M
 // token names an expert at most once).  mode 1: A [T, Kd], C bfloat16 [T*K, Nout] = SwiGLU pair of
 // token t's row under the pair's expert; mode 0: A [T*K, Kd] indexed by pair, C float [T*K, Nout].
 int mi_grouped_gemm_skinny_pairs(const void* A, const int* topk_idx, const void* W, void* C, int T, int K, int E,
-                                 int Nout, int Kd, int mode, cudaStream_t stream) {
+                                 int Nout, int Kd, int mode, int glu_kind, float glu_limit, float glu_slope,
+                                 cudaStream_t stream) {
+    const GluForm glu{glu_kind, glu_limit, glu_slope};
     if (!mi_grouped_gemm_skinny_supported(Kd)) {
         set_last_error("grouped product (decode): inner size %d is not a multiple of 32", Kd);
         return kBadShape;
@@ -481,7 +487,7 @@ int mi_grouped_gemm_skinny_pairs(const void* A, const int* topk_idx, const void*
         const dim3 sgrid((Nout + 15) / 16, compact ? T * K : E);
 #define MI_PAIRS_SPLITK(MODE, COMPACT)                                                                   \
     launch_dependent(grouped_gemm_skinny_pairs_splitk_kernel<MODE, COMPACT>, sgrid, dim3(256), 0, stream, \
-        (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, MODE, Nout, Kd)
+        (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, MODE, Nout, Kd, glu)
         if (mode == 1) { if (compact) MI_PAIRS_SPLITK(1, true); else MI_PAIRS_SPLITK(1, false); }
         else { if (compact) MI_PAIRS_SPLITK(0, true); else MI_PAIRS_SPLITK(0, false); }
 #undef MI_PAIRS_SPLITK
@@ -490,10 +496,10 @@ int mi_grouped_gemm_skinny_pairs(const void* A, const int* topk_idx, const void*
     const dim3 grid((Nout + 63) / 64, E);
     if (mode == 1)
         grouped_gemm_skinny_pairs_kernel<1><<<grid, 128, 0, stream>>>(
-            (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 1, Nout, Kd);
+            (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 1, Nout, Kd, glu);
     else
         grouped_gemm_skinny_pairs_kernel<0><<<grid, 128, 0, stream>>>(
-            (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 0, Nout, Kd);
+            (const __nv_bfloat16*)A, topk_idx, (const __nv_bfloat16*)W, C, T * K, K, 0, Nout, Kd, glu);
     return finish_launch("grouped_gemm_skinny_pairs");
 }
 

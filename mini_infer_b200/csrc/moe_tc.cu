@@ -50,7 +50,7 @@ template <int MODE, int TN, int STAGES, int BLOCKS>
 __global__ void __launch_bounds__(192, BLOCKS)
 grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_constant__ CUtensorMap map_w,
                        const int* __restrict__ offsets, void* __restrict__ C, int E, int Nout, int Kd,
-                       int* __restrict__ status, int skip_kb, uint32_t wait_limit) {
+                       int* __restrict__ status, int skip_kb, uint32_t wait_limit, GluForm glu) {
     // skip_kb >= 0 (tests of the bounded waits only): the producer stops before the loads of that k block, so
     // the wait for them runs out after `wait_limit` rounds, every role gives up and the status word says so.
     constexpr int NB = 2;                                 // weight tiles per stage: gate and up (MODE 1), or two
@@ -180,7 +180,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ RowMaps maps_a, const __grid_cons
                                 const float gv = __uint_as_float(g[i]);
                                 // the result is rounded to bfloat16: the fast exponential and division are exact enough
                                 const __nv_bfloat16 v =
-                                    __float2bfloat16_rn(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[i]));
+                                    __float2bfloat16_rn(glu_join_fast(gv, __uint_as_float(u[i]), glu));
                                 if (staged) st[(size_t)i * BF] = v;
                                 else if (f < Nout) out[(int64_t)i * Nout] = v;
                             }
@@ -242,7 +242,7 @@ template <int MODE, int TN, int STAGES, int NB>
 __global__ void __launch_bounds__(192, 1)
 grouped_gemm_tc_persistent_kernel(const __grid_constant__ RowMaps maps_a, const __grid_constant__ CUtensorMap map_w,
                                   const int* __restrict__ offsets, void* __restrict__ C, int E, int Nout, int Kd,
-                                  int* __restrict__ status) {
+                                  int* __restrict__ status, GluForm glu) {
     constexpr int NW = MODE == 1 ? 2 : NB;                // weight tiles per stage = accumulators per tile
     constexpr int STAGE_BYTES = NW * W_TILE_BYTES + TN * BK * 2;
     constexpr int FEATS = MODE == 1 ? BF : NB * BF;
@@ -415,7 +415,7 @@ grouped_gemm_tc_persistent_kernel(const __grid_constant__ RowMaps maps_a, const 
                             const float gv = __uint_as_float(g[j]);
                             // the result is rounded to bfloat16: the fast exponential and division are exact enough
                             g[j] = (uint32_t)__bfloat16_as_ushort(
-                                __float2bfloat16_rn(__fdividef(gv, 1.0f + __expf(-gv)) * __uint_as_float(u[j])));
+                                __float2bfloat16_rn(glu_join_fast(gv, __uint_as_float(u[j]), glu)));
                         }
                     } else {
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -524,14 +524,17 @@ void mi_grouped_gemm_tc_test_fault(int skip_kb, unsigned int wait_limit) {
 }
 
 // A: [n_rows, Kd] bfloat16, rows sorted by expert (offsets[E+1]); W: [E, wrows, Kd] bfloat16.
-// mode 1: C bfloat16 [n_rows, Nout] = silu(gate) * up with W holding 2*Nout rows per expert;
+// mode 1: C bfloat16 [n_rows, Nout] = glu(gate, up) with W holding 2*Nout rows per expert (glu_kind 0:
+// silu(gate) * up; 1: the bounded form of common.cuh with glu_limit and glu_slope);
 // mode 0: C float [n_rows, Nout].  `status` (device int, zero before the first call) receives a
 // non-zero code if a wait inside the kernel ran out.
 // form: -1 chooses; 0 / 1 one block per tile with row tiles of 128 (two blocks per SM) / 256;
 //       2 / 3 persistent with row tiles of 160 and four pipeline stages / 256 and three.
 int mi_grouped_gemm_tc_form(const void* A, const void* W, const int* offsets, void* C, int* status, int n_rows,
-                            int E, int Nout, int Kd, int mode, int form, cudaStream_t stream) {
+                            int E, int Nout, int Kd, int mode, int form, int glu_kind, float glu_limit,
+                            float glu_slope, cudaStream_t stream) {
     if (n_rows <= 0) return kOk;
+    const GluForm glu{glu_kind, glu_limit, glu_slope};
     if (!mi_grouped_gemm_tc_supported(Kd)) {
         set_last_error("grouped product (tensor cores): inner size %d is not a multiple of %d", Kd, tc::BK);
         return kBadShape;
@@ -594,7 +597,7 @@ int mi_grouped_gemm_tc_form(const void* A, const void* W, const int* offsets, vo
     do {                                                                                              \
         auto kern = tc::grouped_gemm_tc_persistent_kernel<MODE, TN, ST, NB>;                          \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
-        kern<<<blocks, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status);          \
+        kern<<<blocks, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status, glu);     \
     } while (0)
         if (form == 3) { if (mode == 1) MI_TCP_LAUNCH(1, 256, 3, 2); else MI_TCP_LAUNCH(0, 256, 3, 2); }
         else if (mode == 1) MI_TCP_LAUNCH(1, 160, 4, 2);
@@ -615,7 +618,7 @@ int mi_grouped_gemm_tc_form(const void* A, const void* W, const int* offsets, vo
         auto kern = tc::grouped_gemm_tc_kernel<MODE, TN, STAGES, BLOCKS>;                              \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
         kern<<<grid, 192, smem, stream>>>(maps_a, map_w, offsets, C, E, Nout, Kd, status, skip_kb,     \
-                                          wait_limit);                                                 \
+                                          wait_limit, glu);                                            \
     } while (0)
     if (form == 0) {
         if (mode == 1) MI_TC_LAUNCH(1, 128, 2, 2); else MI_TC_LAUNCH(0, 128, 2, 2);
@@ -627,8 +630,10 @@ int mi_grouped_gemm_tc_form(const void* A, const void* W, const int* offsets, vo
 }
 
 int mi_grouped_gemm_tc(const void* A, const void* W, const int* offsets, void* C, int* status, int n_rows, int E,
-                       int Nout, int Kd, int mode, cudaStream_t stream) {
-    return mi_grouped_gemm_tc_form(A, W, offsets, C, status, n_rows, E, Nout, Kd, mode, -1, stream);
+                       int Nout, int Kd, int mode, int glu_kind, float glu_limit, float glu_slope,
+                       cudaStream_t stream) {
+    return mi_grouped_gemm_tc_form(A, W, offsets, C, status, n_rows, E, Nout, Kd, mode, -1, glu_kind, glu_limit,
+                                   glu_slope, stream);
 }
 
 }  // extern "C"

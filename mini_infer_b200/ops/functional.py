@@ -576,12 +576,22 @@ def moe_norm_route_small(hidden: torch.Tensor, delta: Optional[torch.Tensor], no
     return x, idx, w, gate, probs
 
 
+def _glu_args(glu) -> Tuple[int, float, float]:
+    """``glu`` None: the gated units of a paired product are ``silu(gate) * up``; ``(limit, slope)``: the
+    bounded form ``g * logistic(slope * g) * (u + 1)``, ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``."""
+    if glu is None:
+        return 0, 0.0, 0.0
+    limit, slope = glu
+    return 1, float(limit), float(slope)
+
+
 def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,
-                       n_rows: int, swiglu_pair: bool, out_dtype: torch.dtype) -> torch.Tensor:
+                       n_rows: int, swiglu_pair: bool, out_dtype: torch.dtype, glu=None) -> torch.Tensor:
     """Per-expert product of sorted rows (float arithmetic).
 
     ``w`` is ``[E, Nout, K]`` or, with ``swiglu_pair``, ``[E, 2*Nout, K]`` (gate rows,
-    then up rows) and the result is ``silu(gate) * up``.  Row ``r`` of the result
+    then up rows) and the result is ``silu(gate) * up`` (or the bounded form that ``glu`` names,
+    :func:`_glu_args`).  Row ``r`` of the result
     uses ``a[gather[r]]`` (or ``a[r]``) and the expert whose offset range holds ``r``.
     """
     _chk(a, "grouped_gemm a")
@@ -600,7 +610,7 @@ def grouped_gemm_plain(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch
     check(library().mi_grouped_gemm_plain(_ptr(a), _code(a, "grouped_gemm a"), _ptr(gather), _ptr(w),
                                           _code(w, "grouped_gemm w"), _ptr(offsets), _ptr(out),
                                           _code(out, "grouped_gemm out"), int(n_rows), E, nout, Kd,
-                                          1 if swiglu_pair else 0, _stream()), "grouped_gemm_plain")
+                                          1 if swiglu_pair else 0, *_glu_args(glu), _stream()), "grouped_gemm_plain")
     return out
 
 
@@ -649,7 +659,7 @@ def grouped_gemm_skinny_supported(kd: int) -> bool:
 
 
 def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torch.Tensor, offsets: torch.Tensor,
-                        n_rows: int, swiglu_pair: bool) -> torch.Tensor:
+                        n_rows: int, swiglu_pair: bool, glu=None) -> torch.Tensor:
     """The grouped product for a few rows per expert (decode), bfloat16 on tensor cores.
 
     Same contract as :func:`grouped_gemm_plain`; the result is bfloat16 with ``swiglu_pair``
@@ -669,7 +679,7 @@ def grouped_gemm_skinny(a: torch.Tensor, gather: Optional[torch.Tensor], w: torc
         if gather is None and a.shape[0] < n_rows:
             _bad("grouped_gemm_skinny", f"{n_rows} rows wanted, the input has {a.shape[0]}")
     check(library().mi_grouped_gemm_skinny(_ptr(a), _ptr(gather), _ptr(w), _ptr(offsets), _ptr(out), E, nout, Kd,
-                                           1 if swiglu_pair else 0, _stream()), "grouped_gemm_skinny")
+                                           1 if swiglu_pair else 0, *_glu_args(glu), _stream()), "grouped_gemm_skinny")
     return out
 
 
@@ -750,7 +760,7 @@ def skinny_pairs_split_inner_max_tokens() -> int:
 
 
 def grouped_gemm_skinny_pairs(a: torch.Tensor, topk_idx: torch.Tensor, w: torch.Tensor,
-                              swiglu_pair: bool) -> torch.Tensor:
+                              swiglu_pair: bool, glu=None) -> torch.Tensor:
     """The decode-sized grouped product without a permutation: row ``t*K + k`` of the result
     belongs to the pair (token t, slot k) and is computed under expert ``topk_idx[t, k]``.
 
@@ -769,7 +779,8 @@ def grouped_gemm_skinny_pairs(a: torch.Tensor, topk_idx: torch.Tensor, w: torch.
     if DEBUG_BOUNDS:
         _dbg_range(topk_idx, 0, E, "grouped_gemm_skinny_pairs expert indices")
     check(library().mi_grouped_gemm_skinny_pairs(_ptr(a), _ptr(topk_idx), _ptr(w), _ptr(out), T, K, E, nout, Kd,
-                                                 1 if swiglu_pair else 0, _stream()), "grouped_gemm_skinny_pairs")
+                                                 1 if swiglu_pair else 0, *_glu_args(glu), _stream()),
+          "grouped_gemm_skinny_pairs")
     return out
 
 
@@ -799,7 +810,7 @@ TC_FORMS = (0, 1, 2, 3)
 
 
 def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, swiglu_pair: bool,
-                    form: Optional[int] = None) -> torch.Tensor:
+                    form: Optional[int] = None, glu=None) -> torch.Tensor:
     """The grouped product for many rows per expert (prefill): tcgen05 tensor cores fed by TMA.
 
     ``a_sorted [N, K]`` holds the rows already in expert order.  Result as for
@@ -823,7 +834,8 @@ def grouped_gemm_tc(a_sorted: torch.Tensor, w: torch.Tensor, offsets: torch.Tens
         _dbg_offsets(offsets, int(n_rows), "grouped_gemm_tc")
     check(library().mi_grouped_gemm_tc_form(_ptr(a_sorted), _ptr(w), _ptr(offsets), _ptr(out), _ptr(_tc_status[dev]),
                                             n_rows, E, nout, Kd, 1 if swiglu_pair else 0,
-                                            -1 if form is None else int(form), _stream()), "grouped_gemm_tc")
+                                            -1 if form is None else int(form), *_glu_args(glu), _stream()),
+          "grouped_gemm_tc")
     _tc_pending = True
     return out
 

@@ -267,13 +267,9 @@ class SparseMoE(FeedForward):
             return self._run(x, ctx, (idx, w, gate, probs))
         return super().forward_from_residual(hidden, delta, norm, ctx)
 
-    def _gated(self, product) -> torch.Tensor:
-        """The experts' gated units: ``product(True)`` forms ``silu(gate) * up`` in the product's own
-        epilogue; for another activation ``product(False)`` gives the float32 halves and a row-wise kernel
-        joins them."""
-        if self.activation == "silu":
-            return product(True)
-        return F.clamped_glu(product(False), self.limit, self.slope, self.rt.act)
+    def _glu(self):
+        """The form of the experts' gated units, as the grouped products' epilogues take it."""
+        return None if self.activation == "silu" else (self.limit, self.slope)
 
     def _few_rows_per_expert(self, T: int) -> bool:
         """Whether a step of T tokens takes the decode-sized expert products (every used expert's weights
@@ -290,9 +286,8 @@ class SparseMoE(FeedForward):
         return T * self.K <= rows * self.E
 
     def _by_pair(self, T: int) -> bool:
-        """... and without a permutation (result rows indexed by (token, slot) pair).  (The pair-indexed
-        product forms its gated units in its own epilogue, which knows ``silu`` only.)"""
-        return self.activation == "silu" and T <= self._pairs_max and self._few_rows_per_expert(T)
+        """... and without a permutation (result rows indexed by (token, slot) pair)."""
+        return T <= self._pairs_max and self._few_rows_per_expert(T)
 
     def _run(self, x: torch.Tensor, ctx: StepContext, routed) -> WeightedRowSum:
         T = x.shape[0]
@@ -313,7 +308,7 @@ class SparseMoE(FeedForward):
                     want_probs=self.keep_routing, permute=False, bias=self.b_router)
             if overlap and not fork_first:
                 side, shared = self._fork_shared_expert(x)
-            act = self._gated(lambda pair: F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, pair))
+            act = F.grouped_gemm_skinny_pairs(x, idx, self.w_gate_up, True, glu=self._glu())
             y = F.grouped_gemm_skinny_pairs(act, idx, self.w_down, False)
             if ctx.prefetch is not None:
                 # while the experts' rows are summed and normalised, the next layer's first weights arrive
@@ -336,16 +331,16 @@ class SparseMoE(FeedForward):
                 side, shared = self._fork_shared_expert(x)
             if self._few_rows_per_expert(T):
                 # a few rows per expert: bound by reading each used expert once
-                act = self._gated(lambda pair: F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, pair))
+                act = F.grouped_gemm_skinny(x, sorted_token, self.w_gate_up, offsets, n, True, glu=self._glu())
                 y = F.grouped_gemm_skinny(act, None, self.w_down, offsets, n, False)
             elif self._tc:
                 # many rows per expert: tensor-core tiles over the rows gathered into expert order
                 xs = F.gather_rows(x, sorted_token)
-                act = self._gated(lambda pair: F.grouped_gemm_tc(xs, self.w_gate_up, offsets, pair))
+                act = F.grouped_gemm_tc(xs, self.w_gate_up, offsets, True, glu=self._glu())
                 y = F.grouped_gemm_tc(act, self.w_down, offsets, False)
             else:
-                act = self._gated(lambda pair: F.grouped_gemm_plain(
-                    x, sorted_token, self.w_gate_up, offsets, n, pair, self.rt.act if pair else torch.float32))
+                act = F.grouped_gemm_plain(x, sorted_token, self.w_gate_up, offsets, n, True, self.rt.act,
+                                           glu=self._glu())
                 y = F.grouped_gemm_plain(act, None, self.w_down, offsets, n, False, torch.float32)
         if self.keep_routing:
             self.last_routing = (idx, w, probs)

@@ -370,3 +370,46 @@ def test_norm_with_an_offset_gain_and_the_norm_of_the_embedding():
         ref = pn.norm_one_plus((hidden + delta).double(), off.double(), eps)
         assert torch.allclose(out, ref, atol=1e-5 if dtype == "float32" else 3e-2)
         assert torch.allclose(h.cpu(), hidden + delta)
+
+
+@pytest.mark.parametrize("T,E,K,H,I", [(3, 6, 2, 64, 64), (12, 4, 3, 128, 192), (40, 8, 2, 64, 128), (300, 8, 3, 128, 64)])
+def test_bounded_gated_units_inside_every_grouped_product(T, E, K, H, I):
+    """The experts' first product with the bounded gated unit formed in its epilogue: the CUDA-core form in both
+    precisions, the decode-sized forms (sorted rows and by pair) and the tcgen05 form, against a loop over the
+    chosen experts."""
+    limit, slope = 1.3, 1.702
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, 2 * I, H, generator=g) * 2.0 / H ** 0.5).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    want = torch.zeros(T * K, I, dtype=torch.float64)
+    for t in range(T):
+        for k in range(K):
+            gu = w[int(idx[t, k])].double() @ x[t].double()
+            want[t * K + k] = pn.clamped_glu(gu[:I], gu[I:], limit)
+    assert float(want.abs().max()) > 0.9 * limit          # the bound is met
+    offsets, sorted_token, inv_perm = F().moe_permute(idx.to(DEV), E)
+    inv = inv_perm.cpu().long()
+    xd, wd = x.to(DEV), w.to(DEV)
+    got = F().grouped_gemm_plain(xd.float(), sorted_token, wd.float(), offsets, T * K, True, torch.float32,
+                                 glu=(limit, slope)).cpu().double()[inv]
+    assert float((got - want).abs().max()) <= 1e-5 * limit * (limit + 1)
+    tol = 2e-2 * limit * (limit + 1)
+    got = F().grouped_gemm_plain(xd, sorted_token, wd, offsets, T * K, True, torch.bfloat16, glu=(limit, slope))
+    assert float((got.float().cpu().double()[inv] - want).abs().max()) <= tol
+    got = F().grouped_gemm_skinny(xd, sorted_token, wd, offsets, T * K, True, glu=(limit, slope))
+    assert float((got.float().cpu().double()[inv] - want).abs().max()) <= tol
+    if T <= F().skinny_pairs_max_tokens():
+        got = F().grouped_gemm_skinny_pairs(xd, idx.to(DEV), wd, True, glu=(limit, slope))
+        assert float((got.float().cpu().double() - want).abs().max()) <= tol
+    got = F().grouped_gemm_tc(F().gather_rows(xd, sorted_token), wd, offsets, True, glu=(limit, slope))
+    F().check_tc_status()
+    assert float((got.float().cpu().double()[inv] - want).abs().max()) <= tol
+    # without a form the same calls give silu(gate) * up as before
+    got = F().grouped_gemm_skinny(xd, sorted_token, wd, offsets, T * K, True).float().cpu().double()[inv]
+    ref = torch.zeros_like(want)
+    for t in range(T):
+        for k in range(K):
+            gu = w[int(idx[t, k])].double() @ x[t].double()
+            ref[t * K + k] = gu[:I] * torch.sigmoid(gu[:I]) * gu[I:]
+    assert float((got - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
