@@ -634,7 +634,8 @@ def _run_design(args, design, sizes, window, make_config, make_twin, design_work
             for b in range(B):
                 runner.add_request(b)
                 runner.step([StepEntry(b, prompt(), [])])
-            state = {"toks": [1] * B}
+            # a token of its own for every request: rows that are all alike would all pick the same experts
+            state = {"toks": torch.randint(0, V, (B,), generator=g).tolist()}
 
             def decode():
                 res = runner.step([StepEntry(b, [state["toks"][b]], [0]) for b in range(B)])

@@ -18,7 +18,7 @@
 //   warp 1    allocates tensor memory, issues the MMAs
 //   warps 2-5 softmax and epilogue, one lane quarter of tensor memory each
 // S is double-buffered, so the next tile's S = Q K^T runs beside this tile's softmax.  Masking is positional: key j is visible from the
-// query at position p iff j <= p and (window == 0 or j > p - window) and j < kv_len.
+// query at position p iff j <= p and (window == 0 or j > p - window or j < keep_first) and j < kv_len.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out sets an error status that the host
 // reads, lets all roles fall through to the common exit, and the tensor memory is freed there.
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict__ block_table,
                        const int* __restrict__ q_start, const int* __restrict__ kv_len,
                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_pages,
-                       int window, float scale_log2, int* __restrict__ status) {
+                       int window, float scale_log2, int* __restrict__ status, int keep_first) {
     constexpr int DH = D / 64;                            // 64-column halves of a head
     constexpr uint32_t TMEM_COLS = 256;                   // S[0], S[1] (BN columns each), O (D): two blocks share an SM
     constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
@@ -122,7 +122,13 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
     if (window > 0) k_begin = max(0, p_lo - window + 1);
     k_begin = (k_begin / BN) * BN;
     const int k_end = min(kvl, p_hi + 1);
-    const int n_tiles = (k_end - k_begin + BN - 1) / BN;  // >= 1: the query's own key is visible
+    // Behind a window the first keep_first keys of a request stay visible: tiles over [0, sink_end) come
+    // before the window's tiles.  Keys between the two are seen by no query of this block (k_begin is not
+    // above any query's window).
+    const int sink_end = window > 0 ? min(min(keep_first, k_begin), k_end) : 0;
+    const int n_sink = (sink_end + BN - 1) / BN;
+    const int n_tiles = n_sink + (k_end - k_begin + BN - 1) / BN;  // >= 1: the query's own key is visible
+    auto tile_start = [&](int j) { return j < n_sink ? j * BN : k_begin + (j - n_sink) * BN; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = abort_p;
@@ -168,7 +174,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             const int ns = is_k ? NK : NV;
             const int s = j % ns;
             const uint32_t parity = ((j / ns) & 1) ^ 1;
-            const int k0 = k_begin + j * BN;
+            const int k0 = tile_start(j);
             int my_page = -1;                             // looked up before the wait: the latencies overlap
             if (lane < pages_per_tile) {
                 const int kpos = k0 + lane * page_size;
@@ -251,7 +257,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int buf = j & 1;
-            const int k0 = k_begin + j * BN;
+            const int k0 = tile_start(j);
             ok = mbar_wait(&s_full[buf], (j >> 1) & 1, abort_flag, 17);
             ok = __all_sync(0xffffffffu, ok);             // tcgen05.ld and .st are warp-wide: all lanes or none
             if (!ok) break;
@@ -264,12 +270,16 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             // does any (row, key) of this tile need the mask?
             const bool masked = (k0 + BN - 1 > p_lo) || (k0 + BN > kvl) || (window > 0 && k0 < p_hi - window + 1);
+            // below a row's window only kept first keys are visible: of a tile of kept first keys those below
+            // sink_end (such a tile lies below every window, so it is always masked key by key), of a window's
+            // tile those below keep_first
+            const int keep_lim = j < n_sink ? sink_end : keep_first;
             float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of BN steps
             if (masked) {
 #pragma unroll
                 for (int i = 0; i < BN; ++i) {
                     const int kj = k0 + i;
-                    if (kj > vis_hi || kj < vis_lo) v[i] = 0xff800000u;                 // -inf
+                    if (kj > vis_hi || (kj < vis_lo && kj >= keep_lim)) v[i] = 0xff800000u;   // -inf
                     mxs[i & 3] = fmaxf(mxs[i & 3], __uint_as_float(v[i]));
                 }
             } else {
@@ -399,8 +409,9 @@ int mi_attn_prefill_tc_supported(int d, int page_size) {
 int mi_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                        const int* q_start, const int* kv_len, void* out, int* status, int T, int B, int max_q_len,
                        int nh, int nkv, int d, int page_size, int num_pages, int max_pages, int window, float scale,
-                       cudaStream_t stream) {
+                       int keep_first, cudaStream_t stream) {
     if (B <= 0 || max_q_len <= 0 || T <= 0) return kOk;
+    if (keep_first < 0) { set_last_error("prefill attention (tcgen05): %d kept first keys", keep_first); return kBadShape; }
     if (!mi_attn_prefill_tc_supported(d, page_size)) {
         set_last_error("prefill attention (tcgen05): head_dim %d with pages of %d tokens is not taken", d, page_size);
         return kBadShape;
@@ -436,7 +447,8 @@ int mi_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
         auto kern = pt::attn_prefill_tc_kernel<DD>;                                                       \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
         kern<<<grid, 192, smem, stream>>>(maps, block_table, q_start, kv_len, (__nv_bfloat16*)out, nh,    \
-                                          nkv, page_size, max_pages, window, scale_log2, status);         \
+                                          nkv, page_size, max_pages, window, scale_log2, status,          \
+                                          keep_first);                                                    \
     } while (0)
     if (d == 64) MI_PT(64); else MI_PT(128);
 #undef MI_PT

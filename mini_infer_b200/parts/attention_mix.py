@@ -91,6 +91,7 @@ class HeadMixAttention(Mixer):
 
         # bfloat16: scores and P.V on the tensor cores where the kernel is built for the sizes
         self._tensor_cores = rt.act == torch.bfloat16 and F.attention_mix_tc_supported(self.nh, self.nkv, self.dk, self.dv)
+        self._independent_heads = self.mix is None and self.softcap == 0.0 and self.dk == self.dv
 
     def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
         F.l2_prefetch(self.w_qkv)
@@ -124,6 +125,11 @@ class HeadMixAttention(Mixer):
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, 1, self.window,
                                    self.scale, self.softcap, splits, ctx.scratch["attn_mix_part_o"],
                                    ctx.scratch["attn_mix_part_ml"], keep_first=self.keep_first)
+        elif self._independent_heads and F.prefill_attention_tc_supported(self.dk, view.page_size):
+            # heads that exchange nothing, keys and values of one size the tcgen05 kernel is built for: prompt
+            # portions (and what decodes beside them) take the engine's tensor-memory attention
+            a = F.prefill_attention_tc(q, kc, vc, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
+                                       self.window, self.scale, keep_first=self.keep_first)
         else:
             a = F.attention_mix_tc(q, kc, vc, self.mix, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
                                    self.window, self.scale, self.softcap, keep_first=self.keep_first)

@@ -413,3 +413,41 @@ def test_bounded_gated_units_inside_every_grouped_product(T, E, K, H, I):
             gu = w[int(idx[t, k])].double() @ x[t].double()
             ref[t * K + k] = gu[:I] * torch.sigmoid(gu[:I]) * gu[I:]
     assert float((got - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("H,G,d,window,keep,ps", [(4, 2, 64, 40, 4, 16), (8, 2, 128, 300, 1, 16), (6, 3, 64, 9, 70, 8),
+                                                  (2, 1, 128, 64, 64, 32), (3, 3, 64, 130, 17, 64)])
+def test_kept_first_keys_in_the_tensor_memory_attention(H, G, d, window, keep, ps):
+    """The tcgen05 prefill kernel behind a window that keeps the first keys: whole, in portions that start at any
+    place, with single tokens beside them, and with the pages between kept keys and window given back."""
+    assert F().prefill_attention_tc_supported(d, ps)
+    T = 700
+    g = torch.Generator().manual_seed(H + d + keep)
+    q, k, v = (torch.randn(T, n, d, generator=g).to(torch.bfloat16).float() for n in (H, G, G))
+    want = plain_attention(q, k, v, window, keep, d ** -0.5)
+    tol = 1.5e-2 * float(want.abs().max())
+    for cuts, release in (([T], False), ([200, 317, 3, 1, 179], False), ([450, 129, 1, 120], True)):
+        lo, drop = 0, ()
+        if release:
+            lo, cuts = cuts[0], cuts[1:]
+            drop = set(range(-(-keep // ps), max(0, lo - window + 1) // ps))
+        kc, vc, table = paged(k, v, ps, 2 * (-(-T // ps)) + 3, 5, torch.bfloat16, drop)
+        table = i32([table + [-1] * 4])
+        start = lo
+        outs = []
+        for n in cuts:
+            qq = q[lo:lo + n].to(torch.bfloat16).to(DEV).contiguous()
+            outs.append(F().prefill_attention_tc(qq, kc, vc, table, i32([0, n]), i32([lo + n]), n, window, d ** -0.5,
+                                                 keep_first=keep).float().cpu())
+            lo += n
+        F().check_tc_status()
+        got = torch.cat(outs)
+        assert float((got.double() - want[start:]).abs().max()) <= tol, (cuts, release)
+    # a key that stands out among the kept ones, far behind the window
+    for key in (keep - 1, keep):
+        q2, k2, v2 = stand_out(T, H, G, d, d, key, keep, bf16=True)
+        kc, vc, table = paged(k2, v2, ps, 2 * (-(-T // ps)) + 3, 5, torch.bfloat16)
+        got = F().prefill_attention_tc(q2[-5:].to(torch.bfloat16).to(DEV).contiguous(), kc, vc, i32([table]), i32([0, 5]),
+                                       i32([T]), 5, window, 1.0, keep_first=keep).float().cpu()[-1]
+        seen = key < keep or key >= T - window
+        assert torch.allclose(got, v2[key].repeat_interleave(H // G, 0), atol=2e-2) == seen, key
