@@ -79,24 +79,27 @@ struct Maps {
     CUtensorMap q, k, v;
 };
 
-template <int D>
+// DK, DV: key and value sizes in whole 64-column halves (a key row shorter than DK reads zeros beyond its end,
+// in Q and in K alike).  hpq > 1 (with nh = nkv = 1): the heads of a query all read ONE key/value head, so the
+// rows of a tile are (query, head) pairs, hpq consecutive rows a query: q and out are [tokens * hpq, .].
+template <int DK, int DV>
 __global__ void __launch_bounds__(192, 2)
 attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict__ block_table,
                        const int* __restrict__ q_start, const int* __restrict__ kv_len,
                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int page_size, int max_pages,
-                       int window, float scale_log2, int* __restrict__ status, int keep_first) {
-    constexpr int DH = D / 64;                            // 64-column halves of a head
+                       int window, float scale_log2, int* __restrict__ status, int keep_first, int hpq) {
+    constexpr int DKH = DK / 64, DVH = DV / 64;           // 64-column halves of a key and of a value row
     constexpr uint32_t TMEM_COLS = 256;                   // S[0], S[1] (BN columns each), O (D): two blocks share an SM
     constexpr uint32_t COL_S = 0, COL_O = 2 * BN;
     // instruction descriptors: D float32, A and B bfloat16, M = 128
     constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((128u >> 4) << 24);
-    constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) |
+    constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(DV >> 3) << 17) |
                                   ((128u >> 4) << 24);    // B (the V tile) MN-major
     extern __shared__ __align__(1024) uint8_t smem[];     // tiles first (the swizzle wants 1024-byte alignment)
-    uint8_t* sQ = smem;                                   // DH halves of [128 queries][64]
-    uint8_t* sK = sQ + DH * HALF_BYTES;                   // NK stages of DH halves of [BN keys][64]
-    uint8_t* sV = sK + NK * DH * KV_HALF;                 // NV stages of the same for V
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NV * DH * KV_HALF);
+    uint8_t* sQ = smem;                                   // DKH halves of [128 queries][64]
+    uint8_t* sK = sQ + DKH * HALF_BYTES;                  // NK stages of DKH halves of [BN keys][64]
+    uint8_t* sV = sK + NK * DKH * KV_HALF;                // NV stages of DVH halves for V
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + NV * DVH * KV_HALF);
     uint64_t* q_full = bars;                              // then the barriers and a few words
     uint64_t* k_full = bars + 1;
     uint64_t* v_full = k_full + NK;
@@ -111,13 +114,13 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
 
     // later query tiles see more keys: they are launched first, so that the short ones fill the tail
     const int b = blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
-    const int q0 = q_start[b], q_len = q_start[b + 1] - q0;
+    const int q0 = q_start[b] * hpq, q_len = (q_start[b + 1] - q_start[b]) * hpq;      // in rows
     if (qt * BQ >= q_len) return;                         // uniform for the whole block
     const int kvl = kv_len[b];
     const int hk = h / (nh / nkv);
     const int nq = min(BQ, q_len - qt * BQ);
-    const int p_lo = kvl - q_len + qt * BQ;               // position of the tile's first query
-    const int p_hi = p_lo + nq - 1;
+    const int p_lo = kvl - q_len / hpq + (qt * BQ) / hpq; // position of the tile's first query (hpq divides BQ)
+    const int p_hi = p_lo + (nq - 1) / hpq;
     int k_begin = 0;
     if (window > 0) k_begin = max(0, p_lo - window + 1);
     k_begin = (k_begin / BN) * BN;
@@ -144,7 +147,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
     }
     // Key and value stages start as zeros: rows that no copy fills (pages a window has released, the
     // end of the last tile) are masked in S, and P = 0 times a finite stale value is 0.
-    for (int i = threadIdx.x; i < (NK + NV) * DH * KV_HALF / 16; i += blockDim.x)
+    for (int i = threadIdx.x; i < (NK * DKH + NV * DVH) * KV_HALF / 16; i += blockDim.x)
         reinterpret_cast<uint4*>(sK)[i] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == 1) {
@@ -159,19 +162,20 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(q_full, DH * HALF_BYTES);
-            for (int hh = 0; hh < DH; ++hh)
-                tma_load_2d(sQ + hh * HALF_BYTES, &maps.q, h * D + hh * 64, q0 + qt * BQ, q_full);
+            mbar_expect_tx(q_full, DKH * HALF_BYTES);
+            for (int hh = 0; hh < DKH; ++hh)
+                tma_load_2d(sQ + hh * HALF_BYTES, &maps.q, h * DK + hh * 64, q0 + qt * BQ, q_full);
         }
         const int* table = block_table + (int64_t)b * max_pages;
         const int pages_per_tile = BN / page_size;
         const uint32_t page_bytes = (uint32_t)page_size * 128u;
-        const int items = pages_per_tile * DH;            // page x 64-column half: one copy each
         // One tile of K or of V: wait for its stage, look its pages up, copy those that exist (inside the
         // request, not released by a window).  A K stage is free once S = Q K^T of two tiles before has
         // run, a V stage once O += P V of two tiles before has: K runs a tile ahead of V.
         auto load_tile = [&](int j, bool is_k) -> bool {
             const int ns = is_k ? NK : NV;
+            const int halves = is_k ? DKH : DVH;
+            const int items = pages_per_tile * halves;    // page x 64-column half: one copy each
             const int s = j % ns;
             const uint32_t parity = ((j / ns) & 1) ^ 1;
             const int k0 = tile_start(j);
@@ -186,14 +190,14 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             const unsigned have = __ballot_sync(0xffffffffu, my_page >= 0);
             if (lane < pages_per_tile) tile_pages[lane] = my_page;
             uint64_t* bar = is_k ? &k_full[s] : &v_full[s];
-            if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(have) * page_bytes * DH);
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)__popc(have) * page_bytes * halves);
             __syncwarp();
             for (int it = lane; it < items; it += 32) {
-                const int pg = it / DH, hh = it - pg * DH;
+                const int pg = it / halves, hh = it - pg * halves;
                 const int page = tile_pages[pg];
                 if (page < 0) continue;
                 const int row = (page * nkv + hk) * page_size;
-                uint8_t* dst = (is_k ? sK : sV) + (size_t)s * DH * KV_HALF + hh * KV_HALF + (size_t)pg * page_bytes;
+                uint8_t* dst = (is_k ? sK : sV) + (size_t)s * halves * KV_HALF + hh * KV_HALF + (size_t)pg * page_bytes;
                 tma_load_2d(dst, is_k ? &maps.k : &maps.v, hh * 64, row, bar);
             }
             __syncwarp();                                 // tile_pages is rewritten by the next call
@@ -215,9 +219,9 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                 const int s = j % NK, buf = j & 1;
                 if (!mbar_wait(&k_full[s], (j / NK) & 1, abort_flag, 13)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t dks = umma_desc(smem_u32(sK + (size_t)s * DH * KV_HALF));
+                const uint64_t dks = umma_desc(smem_u32(sK + (size_t)s * DKH * KV_HALF));
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
+                for (int kk = 0; kk < DK / 16; ++kk) {
                     const uint32_t sub = (uint32_t)(kk & 3) * 32;
                     umma_bf16(tmem_base + COL_S + buf * BN, dq + (((uint32_t)(kk >> 2) * HALF_BYTES + sub) >> 4),
                               dks + (((uint32_t)(kk >> 2) * KV_HALF + sub) >> 4), IDESC_S, kk > 0 ? 1u : 0u);
@@ -234,7 +238,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
                      mbar_wait(&v_full[s], (j / NV) & 1, abort_flag, 16);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t dvs = umma_desc_mn(smem_u32(sV + (size_t)s * DH * KV_HALF), KV_HALF);
+                const uint64_t dvs = umma_desc_mn(smem_u32(sV + (size_t)s * DVH * KV_HALF), KV_HALF);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)     // 16 keys of P are 8 columns of tensor memory
                     umma_bf16_tmem_a(tmem_base + COL_O, tmem_base + COL_S + buf * BN + ks * 8,
@@ -249,7 +253,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const int p_row = p_lo + r;                       // position of this thread's query
+        const int p_row = p_lo + r / hpq;                 // position of this thread's query
         const int vis_hi = min(p_row, kvl - 1);           // last visible key
         const int vis_lo = window > 0 ? p_row - window + 1 : 0;   // first visible key
         float m_ref = -INFINITY;                          // reference of the exponentials, in log2 units
@@ -314,7 +318,7 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
             if (rescale) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-                for (int c0 = 0; c0 < D; c0 += 32) {
+                for (int c0 = 0; c0 < DV; c0 += 32) {
                     uint32_t o[32];
                     tmem_ld32(lane_addr + COL_O + c0, o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -346,9 +350,9 @@ attn_prefill_tc_kernel(const __grid_constant__ Maps maps, const int* __restrict_
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            __nv_bfloat16* dst = out + ((int64_t)(q0 + qt * BQ + r) * nh + h) * D;
+            __nv_bfloat16* dst = out + ((int64_t)(q0 + qt * BQ + r) * nh + h) * DV;
 #pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = 0; c0 < DV; c0 += 32) {
                 uint32_t o[32];
                 tmem_ld32(lane_addr + COL_O + c0, o);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -444,14 +448,69 @@ int mi_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, 
     const size_t smem = (size_t)dh * pt::HALF_BYTES + (size_t)(pt::NK + pt::NV) * dh * pt::KV_HALF + 256;
 #define MI_PT(DD)                                                                                         \
     do {                                                                                                  \
-        auto kern = pt::attn_prefill_tc_kernel<DD>;                                                       \
+        auto kern = pt::attn_prefill_tc_kernel<DD, DD>;                                                   \
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
         kern<<<grid, 192, smem, stream>>>(maps, block_table, q_start, kv_len, (__nv_bfloat16*)out, nh,    \
                                           nkv, page_size, max_pages, window, scale_log2, status,          \
-                                          keep_first);                                                    \
+                                          keep_first, 1);                                                 \
     } while (0)
     if (d == 64) MI_PT(64); else MI_PT(128);
 #undef MI_PT
+    return finish_launch("attn_prefill_tc");
+}
+
+// The same kernel for heads that all read ONE key/value head whose values are the first `dv` numbers of its key
+// rows (attention through a latent with the key matrices folded into the queries): q [T, H, dk], cache one layer's
+// [num_pages, 1, page_size, dk], out [T, H, dv] bfloat16.  The rows of a query tile are (query, head) pairs, so
+// a key tile is fetched once for all heads.  Takes H a divisor of 128, dv 64 or 128, dk a multiple of 8 of at
+// most 256 (rounded up to whole 64-column halves that read zeros beyond dk) and the page sizes of the kernel.
+int mi_attn_prefill_tc_shared_supported(int H, int dk, int dv, int page_size) {
+    return H >= 1 && H <= 128 && 128 % H == 0 && (dv == 64 || dv == 128) && dk >= dv && dk <= 256 && dk % 8 == 0 &&
+           mi_attn_prefill_tc_supported(64, page_size);
+}
+
+int mi_attn_prefill_tc_shared(const void* q, const void* cache, const int* block_table, const int* q_start,
+                              const int* kv_len, void* out, int* status, int T, int B, int max_q_len, int H, int dk,
+                              int dv, int page_size, int num_pages, int max_pages, int window, float scale,
+                              int keep_first, cudaStream_t stream) {
+    if (B <= 0 || max_q_len <= 0 || T <= 0) return kOk;
+    if (!mi_attn_prefill_tc_shared_supported(H, dk, dv, page_size) || keep_first < 0) {
+        set_last_error("prefill attention over a shared head (tcgen05): %d heads, rows of %d, values of %d, pages of %d "
+                       "tokens are not taken", H, dk, dv, page_size);
+        return kBadShape;
+    }
+    if (B > 65535) { set_last_error("attention: batch %d exceeds the grid limit 65535", B); return kBadShape; }
+    if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(cache) | reinterpret_cast<uintptr_t>(out)) & 15) {
+        set_last_error("prefill attention (tcgen05): operands must be 16-byte aligned");
+        return kBadShape;
+    }
+    pt::Maps maps;
+    const uint64_t cache_rows = (uint64_t)num_pages * page_size;
+    bool ok = pt::make_map_pitched(&maps.q, q, (uint64_t)T * H, (uint64_t)dk, (uint64_t)dk, pt::BQ) &&
+              pt::make_map_pitched(&maps.k, cache, cache_rows, (uint64_t)dk, (uint64_t)dk, (uint32_t)page_size) &&
+              pt::make_map_pitched(&maps.v, cache, cache_rows, (uint64_t)dv, (uint64_t)dk, (uint32_t)page_size);
+    if (!ok) {
+        set_last_error("prefill attention (tcgen05): cuTensorMapEncodeTiled failed");
+        return kLaunchFailed;
+    }
+    const int DKr = (dk + 63) / 64 * 64;
+    const dim3 grid(((int64_t)max_q_len * H + pt::BQ - 1) / pt::BQ, 1, B);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const size_t smem = (size_t)(DKr / 64) * pt::HALF_BYTES +
+                        (size_t)(pt::NK * (DKr / 64) + pt::NV * (dv / 64)) * pt::KV_HALF + 256;
+#define MI_PTS(KK, VV)                                                                                    \
+    do {                                                                                                  \
+        auto kern = pt::attn_prefill_tc_kernel<KK, VV>;                                                   \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);               \
+        kern<<<grid, 192, smem, stream>>>(maps, block_table, q_start, kv_len, (__nv_bfloat16*)out, 1, 1,  \
+                                          page_size, max_pages, window, scale_log2, status, keep_first, H); \
+    } while (0)
+    if (dv == 64) {
+        if (DKr == 64) MI_PTS(64, 64); else if (DKr == 128) MI_PTS(128, 64); else if (DKr == 192) MI_PTS(192, 64); else MI_PTS(256, 64);
+    } else {
+        if (DKr == 128) MI_PTS(128, 128); else if (DKr == 192) MI_PTS(192, 128); else MI_PTS(256, 128);
+    }
+#undef MI_PTS
     return finish_launch("attn_prefill_tc");
 }
 

@@ -389,6 +389,42 @@ def prefill_attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     return out
 
 
+def prefill_attention_tc_shared_supported(heads: int, dk: int, dv: int, page_size: int) -> bool:
+    return bool(library().mi_attn_prefill_tc_shared_supported(int(heads), int(dk), int(dv), int(page_size)))
+
+
+def prefill_attention_tc_shared(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
+                                kv_len: torch.Tensor, max_q_len: int, window: int, scale: float, value_dim: int,
+                                keep_first: int = 0) -> torch.Tensor:
+    """:func:`prefill_attention_tc` for heads that all read ONE key/value head whose values are the first
+    ``value_dim`` numbers of its key rows: ``q [T, H, dk]``, ``cache [pages, 1, page_size, dk]``, result
+    ``[T, H, value_dim]``.  The rows of a query tile are (query, head) pairs, so a tile of keys is fetched once
+    for all heads.  Sizes: :func:`prefill_attention_tc_shared_supported`."""
+    global _tc_pending
+    _chk(q, "prefill_attention_tc_shared q", BF16)
+    T, H, dk = q.shape
+    _chk(cache, "prefill_attention_tc_shared cache", BF16, (None, 1, None, dk))
+    num_pages, _, page_size, _ = cache.shape
+    _chk(block_table, "prefill_attention_tc_shared block_table", I32)
+    B, max_pages = block_table.shape
+    _chk(q_start, "prefill_attention_tc_shared q_start", I32, (B + 1,))
+    _chk(kv_len, "prefill_attention_tc_shared kv_len", I32, (B,))
+    out = torch.empty(T, H, int(value_dim), dtype=BF16, device=q.device)
+    dev = q.device
+    if dev not in _tc_status:
+        _tc_status[dev] = torch.zeros(1, dtype=I32, device=dev)
+    if DEBUG_BOUNDS:
+        _dbg_batch("prefill_attention_tc_shared", q_start, kv_len, block_table, T, num_pages, page_size, int(window),
+                   int(max_q_len))
+    check(library().mi_attn_prefill_tc_shared(_ptr(q), _ptr(cache), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
+                                              _ptr(out), _ptr(_tc_status[dev]), T, B, int(max_q_len), H, dk,
+                                              int(value_dim), page_size, num_pages, max_pages, int(window),
+                                              float(scale), int(keep_first), _stream()),
+          "prefill_attention_tc_shared")
+    _tc_pending = True
+    return out
+
+
 def decode_attention_supported(d: int) -> bool:
     return bool(library().mi_attn_decode_supported(int(d)))
 

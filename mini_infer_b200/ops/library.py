@@ -58,6 +58,7 @@ _SIGNATURES = {
     "mi_geglu_tanh": [P, P, I, L, I, P],
     "mi_concat_cast": [P, P, P, P, P, I, I, I, P],
     "mi_rows_plus_vec": [P, P, P, I, I, I, P],
+    "mi_attn_prefill_tc_shared": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P],
     "mi_clamped_glu": [P, P, I, L, I, F, F, P],
     "mi_dense_f32_batched": [P, P, P, I, I, I, I, I, I, L, L, L, P],
     "mi_latent_store": [P, I, I, P, P, P, F, P, P, I, I, I, I, P],
@@ -119,6 +120,8 @@ def library() -> ctypes.CDLL:
     lib.mi_attn_mix_tc_splits.restype = c_int
     lib.mi_attn_mix_supported.argtypes = [I, I, I, I, I]
     lib.mi_attn_mix_supported.restype = c_int
+    lib.mi_attn_prefill_tc_shared_supported.argtypes = [I, I, I, I]
+    lib.mi_attn_prefill_tc_shared_supported.restype = c_int
     lib.mi_attn_decode_split_size.argtypes = []
     lib.mi_attn_decode_split_size.restype = c_int
     _lib = lib

@@ -146,6 +146,11 @@ class LatentAttention(Mixer):
             a = F.attention_mix_tc(q_full, rows, rows, None, view.block_table, ctx.q_start, ctx.kv_len, 1, self.window,
                                    self.scale, 0.0, splits, ctx.scratch["attn_mix_part_o"],
                                    ctx.scratch["attn_mix_part_ml"], value_dim=c)
+        elif F.prefill_attention_tc_shared_supported(H, c + r, c, view.page_size):
+            # prompt portions (and what decodes beside them): the tensor-memory attention with (query, head)
+            # pairs as the rows of a tile
+            a = F.prefill_attention_tc_shared(q_full, rows, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
+                                              self.window, self.scale, c)
         else:
             a = F.attention_mix_tc(q_full, rows, rows, None, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,
                                    self.window, self.scale, 0.0, value_dim=c)

@@ -451,3 +451,43 @@ def test_kept_first_keys_in_the_tensor_memory_attention(H, G, d, window, keep, p
                                        i32([T]), 5, window, 1.0, keep_first=keep).float().cpu()[-1]
         seen = key < keep or key >= T - window
         assert torch.allclose(got, v2[key].repeat_interleave(H // G, 0), atol=2e-2) == seen, key
+
+
+@pytest.mark.parametrize("H,c,r,window,ps", [(4, 64, 16, 24, 8), (16, 128, 64, 300, 16), (8, 128, 32, 17, 16), (1, 64, 8, 0, 32),
+                                             (32, 64, 64, 1000, 64), (2, 128, 128, 129, 8)])
+def test_heads_that_share_one_key_value_head_in_the_tensor_memory_attention(H, c, r, window, ps):
+    """(query, head) pairs as the rows of a query tile; values are the leading part of the key rows; key rows
+    that end inside a 64-column half."""
+    assert F().prefill_attention_tc_shared_supported(H, c + r, c, ps)
+    assert not F().prefill_attention_tc_shared_supported(6, c + r, c, ps)
+    T = 700
+    g = torch.Generator().manual_seed(H + c + r)
+    rows = torch.randn(T, 1, c + r, generator=g).to(torch.bfloat16).float()
+    q = (torch.randn(T, H, c + r, generator=g) * 0.5).to(torch.bfloat16).float()
+    scale = (c + r) ** -0.5
+    want = pn.masked_softmax_attention(q.double(), rows.double(), rows.double()[..., :c], scale, pn.visible(T, window or T))
+    tol = 1.5e-2 * float(want.abs().max())
+    for cuts, release in (([T], False), ([200, 317, 3, 1, 179], False), ([450, 129, 1, 120], True)):
+        lo, drop = 0, ()
+        if release:
+            lo, cuts = cuts[0], cuts[1:]
+            if window:
+                drop = set(range(0, max(0, lo - window + 1) // ps))
+        cache, _, table = paged(rows, rows, ps, 2 * (-(-T // ps)) + 3, 9, torch.bfloat16, drop)
+        table = i32([table + [-1] * 4])
+        start, outs = lo, []
+        for n in cuts:
+            qq = q[lo:lo + n].to(torch.bfloat16).to(DEV).contiguous()
+            outs.append(F().prefill_attention_tc_shared(qq, cache, table, i32([0, n]), i32([lo + n]), n, window, scale, c).float().cpu())
+            lo += n
+        F().check_tc_status()
+        got = torch.cat(outs)
+        assert got.shape == (T - start, H, c)
+        assert float((got.double() - want[start:]).abs().max()) <= tol, (cuts, release)
+    # two requests of unequal portions in one launch
+    cache, _, table = paged(rows, rows, ps, 2 * (-(-T // ps)) + 3, 9, torch.bfloat16)
+    qq = torch.cat([q[100:130], q[699:700]]).to(torch.bfloat16).to(DEV).contiguous()
+    got = F().prefill_attention_tc_shared(qq, cache, i32([table, table]), i32([0, 30, 31]), i32([130, 700]), 30, window,
+                                          scale, c).float().cpu().double()
+    F().check_tc_status()
+    assert float((got[:30] - want[100:130]).abs().max()) <= tol and float((got[30] - want[699]).abs().max()) <= tol
