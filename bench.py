@@ -721,6 +721,8 @@ def _nipapel_kernel_work(cfg, T, B, ctx, decode):
     (prefill of T tokens of one request, or a decode step of B requests at context ctx)."""
     rows = B if decode else T
     out = {}
+    # decode steps take the split kernel; prompt portions the tensor-memory attention where the sizes allow
+    attention_kernels = ("attn_mix_tc_kernel",) if decode else ("attn_mix_tc_kernel", "pt::attn_prefill_tc_kernel")
 
     def add(name, by, fl):
         a = out.setdefault(name, [0.0, 0.0])
@@ -734,12 +736,14 @@ def _nipapel_kernel_work(cfg, T, B, ctx, decode):
         if L["type"] == "attention":
             H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
             by = (B * keys * G * (d + e) * 2 + B * H * (d + e) * 2) if decode else T * (H + G) * (d + e) * 2
-            add("attn_mix_tc_kernel", by, pairs * H * (2.0 * d + 2.0 * e))
+            for name in attention_kernels:
+                add(name, by, pairs * H * (2.0 * d + 2.0 * e))
             add("rope_store_kernel", rows * (H * d + G * (d + e)) * 6, 0)
         else:
             H, d, r, e, c = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
             by = (B * keys * (c + r) * 2 + B * H * (2 * c + r) * 2) if decode else T * (H * (2 * c + r) + c + r) * 2
-            add("attn_mix_tc_kernel", by, pairs * H * (2.0 * (c + r) + 2.0 * c))
+            for name in attention_kernels:
+                add(name, by, pairs * H * (2.0 * (c + r) + 2.0 * c))
             if m.get("kv_from") is None:
                 add("latent_store_kernel", rows * (c + r) * 6, 0)
             add("latent_query_kernel", rows * H * ((d + r) * 4 + (d + r) * 2), 0)

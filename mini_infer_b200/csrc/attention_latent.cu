@@ -90,6 +90,33 @@ sigmoid_gate_kernel(const AT* __restrict__ a, int64_t a_head, int64_t a_tok, con
     }
 }
 
+// bfloat16 with e a multiple of 8 and 16-byte aligned rows: eight gated values per thread
+__global__ void __launch_bounds__(256)
+sigmoid_gate_bf16x8_kernel(const __nv_bfloat16* __restrict__ a, int64_t a_head, int64_t a_tok,
+                           const float* __restrict__ g, int ldg, int col0, __nv_bfloat16* __restrict__ out, int T,
+                           int H, int e8) {
+    wait_for_earlier_kernels();
+    const int64_t total = (int64_t)T * H * e8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int j = (int)(idx % e8) * 8;
+        const int h = (int)((idx / e8) % H);
+        const int64_t t = idx / ((int64_t)e8 * H);
+        const uint4 av = __ldg(reinterpret_cast<const uint4*>(a + h * a_head + t * a_tok + j));
+        const float4* gp = reinterpret_cast<const float4*>(g + t * ldg + col0 + h * (e8 * 8) + j);
+        const float4 g0 = __ldg(gp), g1 = __ldg(gp + 1);
+        const __nv_bfloat162* ap = reinterpret_cast<const __nv_bfloat162*>(&av);
+        const float z[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        uint4 o;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 x = __bfloat1622float2(ap[k]);
+            op[k] = __floats2bfloat162_rn(x.x / (1.0f + expf(-z[2 * k])), x.y / (1.0f + expf(-z[2 * k + 1])));
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = o;
+    }
+}
+
 }  // namespace mi
 
 using namespace mi;
@@ -131,6 +158,14 @@ int mi_sigmoid_gate(const void* a, int64_t a_head, int64_t a_tok, const float* g
         return kBadShape;
     }
     const int64_t total = (int64_t)T * H * e;
+    if (adtype == kBF16 && e % 8 == 0 && a_head % 8 == 0 && a_tok % 8 == 0 && ldg % 4 == 0 && col0 % 4 == 0 &&
+        ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        int64_t vblocks = (total / 8 + 255) / 256;
+        if (vblocks > 148 * 16) vblocks = 148 * 16;
+        launch_dependent(sigmoid_gate_bf16x8_kernel, dim3((int)vblocks), dim3(256), 0, stream,
+                         (const __nv_bfloat16*)a, a_head, a_tok, g, ldg, col0, (__nv_bfloat16*)out, T, H, e / 8);
+        return finish_launch("sigmoid_gate");
+    }
     const int blocks = (int)((total + 255) / 256 < 65535 ? (total + 255) / 256 : 65535);
     MI_DISPATCH_1(adtype, AT,
         launch_dependent(sigmoid_gate_kernel<AT>, dim3(blocks), dim3(256), 0, stream, (const AT*)a, a_head, a_tok, g,

@@ -101,6 +101,9 @@ class LatentAttention(Mixer):
             raise ValueError(f"latent attention: {self.nh} heads over rows of {dk} with values of {self.c} "
                              f"are more than one block of the kernel holds")
         self._tensor_cores = rt.act == torch.bfloat16 and F.attention_mix_tc_supported(self.nh, 1, dk, self.c)
+        # prompt portions on the tensor-memory attention: its blocks want whole SMs (a block arrangement that
+        # runs another part beside this one asks)
+        self.large_steps_fill_the_device = self._tensor_cores
 
     def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
         F.l2_prefetch(self.w_dq)

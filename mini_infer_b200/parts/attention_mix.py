@@ -92,6 +92,9 @@ class HeadMixAttention(Mixer):
         # bfloat16: scores and P.V on the tensor cores where the kernel is built for the sizes
         self._tensor_cores = rt.act == torch.bfloat16 and F.attention_mix_tc_supported(self.nh, self.nkv, self.dk, self.dv)
         self._independent_heads = self.mix is None and self.softcap == 0.0 and self.dk == self.dv
+        # prompt portions on the tensor-memory attention: its blocks want whole SMs (a block arrangement that
+        # runs another part beside this one asks)
+        self.large_steps_fill_the_device = self._tensor_cores and self._independent_heads
 
     def prefetch_first(self, ctx: StepContext, cache: Optional[CacheBinding]) -> None:
         F.l2_prefetch(self.w_qkv)

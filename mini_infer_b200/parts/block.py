@@ -143,7 +143,10 @@ class ParallelResidual(Block):
         else:
             x1 = apply_norm(n1, hidden, pending)
             x2 = apply_norm(n2, hidden, None)
-        if not (TUNING.parallel_residual_two_streams and x1.is_cuda):
+        two_streams = TUNING.parallel_residual_two_streams and x1.is_cuda
+        if two_streams and getattr(layer.mixer, "large_steps_fill_the_device", False):
+            two_streams = ctx.num_tokens <= TUNING.parallel_residual_two_streams_max_tokens_full_sm_mixer
+        if not two_streams:
             y = layer.mixer.forward(x1, ctx, caches.get("mixer"))
             return TensorSum(y, layer.feed_forward.forward(x2, ctx))
         # the two branches share nothing but the residual they read: the feed-forward goes to a second stream

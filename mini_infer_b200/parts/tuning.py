@@ -97,6 +97,13 @@ class Tuning:
     # a second stream beside the mixer: a recurrent mixer walks a prompt with a few warps per SM and the
     # feed-forward's products fill the rest; in a decode step the two chains of small kernels run side by side.
     parallel_residual_two_streams: bool = True
+    # ... unless the mixer's kernels of a large step want whole SMs themselves (tensor-memory attention: its
+    # blocks and those of the feed-forward's tensor-core products cannot sit on one SM, and a block that
+    # finds the tensor memory taken waits at its allocation).  One prompt of 2,048 tokens, mixer and routed
+    # feed-forward both on tcgen05 kernels: 2.65 ms on two streams against 2.07 ms on one at width 1,024
+    # (3.23 against 3.42 ms at width 2,048); decode steps of 8 requests gain on two streams at both sizes
+    # (0.357 against 0.443 ms, 0.785 against 0.865 ms).
+    parallel_residual_two_streams_max_tokens_full_sm_mixer: int = 256
 
     def decode_graph_batch(self, num_requests: int) -> int:
         if num_requests <= self.decode_graph_exact_batch_max:
