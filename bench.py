@@ -575,12 +575,15 @@ def run_vizalix(args):
                        "dense_twin")
 
 
-def _run_design(args, design, sizes, window, make_config, make_twin, design_work, twin_work, twin_name):
+def _run_design(args, design, sizes, window, make_config, make_twin, design_work, twin_work, twin_name,
+                graph_prompts=False):
     """A design beside the closest built-in model: prefill and decode throughput at sizes that resemble a real
     model's layers (random weights), with the device time of every kernel of one step of each and, for the
     kernels that the work functions name, the share of the roofline (the slower of algorithmic bytes over the
     measured copy bandwidth and operations over the measured bf16 product rate).  Prints one JSON line; the
-    default workload of this file is not touched."""
+    default workload of this file is not touched.  ``graph_prompts``: the prompt's step is replayed from a
+    captured pass, as the engine does for the full portions of a long prompt (a step of a small model is
+    otherwise bound by the host's launches, not by the device)."""
     import torch
     from mini_infer_b200.engine.defaults import DEFAULT_PAGE_SIZE
     from mini_infer_b200.engine.loading import random_model
@@ -599,7 +602,7 @@ def _run_design(args, design, sizes, window, make_config, make_twin, design_work
             model, rt = random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0")
             runner = ModelRunner(model, rt, page_size=page, num_pages=(B + 1) * (-(-(ctx + 512) // page)) + 8,
                                  max_requests=max(B, 2), max_tokens_per_step=max(T, B), max_context=ctx + 512,
-                                 cuda_graphs=not args.eager)
+                                 cuda_graphs=not args.eager, graph_chunk_tokens=T if graph_prompts and not args.eager else 0)
             g = torch.Generator().manual_seed(args.seed)
             V = cfg.get("vocab", cfg.get("vocab_size"))
 
@@ -771,7 +774,7 @@ def _moe_twin_kernel_work(cfg, size, window, T, B, ctx, decode):
 
 def run_nipapel(args):
     return _run_design(args, "nipapel", args.nipapel, args.nipapel_window, nipapel_config, moe_twin_config,
-                       _nipapel_kernel_work, _moe_twin_kernel_work, "moe_twin")
+                       _nipapel_kernel_work, _moe_twin_kernel_work, "moe_twin", graph_prompts=True)
 
 
 def run_reference(args):

@@ -139,7 +139,8 @@ class LatentAttention(Mixer):
         if f32:
             F.dense_f32_heads(q, self.w_uk_fold, out=q_full, x_head_stride=d + r, out_head_stride=c + r)
         else:
-            q_full[:, :, :c].copy_(torch.bmm(q_plain.transpose(0, 1), self.w_uk_fold).transpose(0, 1))
+            # written head by head into its place before the rotated parts (rows H * (c + r) apart)
+            torch.bmm(q_plain.transpose(0, 1), self.w_uk_fold, out=q_full.transpose(0, 1)[:, :, :c])
         # one shared key/value head: keys are the cached rows, values their first c numbers
         if not self._tensor_cores:
             a = F.attention_mix(q_full, rows, rows, None, view.block_table, ctx.q_start, ctx.kv_len, ctx.max_q_len,

@@ -19,7 +19,7 @@ from ..config.registry import part_class, register_part
 from ..ops import functional as F
 from .tuning import TUNING
 from .base import (Block, BuiltLayer, CacheBinding, Embedding, LMHead, Runtime, StepContext, TensorDecl, TensorSum,
-                   apply_norm, linear, split_sum)
+                   WeightedRowSum, apply_norm, linear, resolve, split_sum)
 
 
 class PreNormResidual(Block):
@@ -124,6 +124,7 @@ class ParallelResidual(Block):
         self.has_ff = bool(self.params.get("feed_forward", True))
         self.shared_norm = bool(self.params.get("shared_norm", False))
         self._side_stream = None
+        self._ones = None
         self.roles = {"mixer_norm": "norm", "mixer": "mixer"}
         if self.has_ff:
             self.roles.update({"feed_forward": "feed_forward"} if self.shared_norm else
@@ -148,7 +149,7 @@ class ParallelResidual(Block):
             two_streams = ctx.num_tokens <= TUNING.parallel_residual_two_streams_max_tokens_full_sm_mixer
         if not two_streams:
             y = layer.mixer.forward(x1, ctx, caches.get("mixer"))
-            return TensorSum(y, layer.feed_forward.forward(x2, ctx))
+            return self._sum(y, layer.feed_forward.forward_deferred(x2, ctx))
         # the two branches share nothing but the residual they read: the feed-forward goes to a second stream
         main = torch.cuda.current_stream()
         if self._side_stream is None:
@@ -157,11 +158,25 @@ class ParallelResidual(Block):
         side.wait_stream(main)
         x2.record_stream(side)
         with torch.cuda.stream(side):
-            f = layer.feed_forward.forward(x2, ctx)
-        f.record_stream(main)
+            f = layer.feed_forward.forward_deferred(x2, ctx)
+        for t in (f.rows, f.index, f.weights, f.extra, f.scale) if isinstance(f, WeightedRowSum) else (f,):
+            if t is not None:
+                t.record_stream(main)
         y = layer.mixer.forward(x1, ctx, caches.get("mixer"))
         main.wait_stream(side)
-        return TensorSum(y, f)
+        return self._sum(y, f)
+
+    def _sum(self, y: torch.Tensor, f):
+        """The two parts' outputs as one pending sum.  A feed-forward that leaves the weighted sum of its
+        experts' rows to the next norm's kernel (and has no shared expert in the place of the sum's extra
+        term) takes the mixer's output along as that term, with a weight of one: the norm's kernel then adds
+        both while it reads the row anyway."""
+        if isinstance(f, WeightedRowSum) and f.extra is None:
+            T = y.shape[0]
+            if self._ones is None or self._ones.numel() < T or self._ones.device != y.device:
+                self._ones = torch.ones(max(T, 1024), dtype=torch.float32, device=y.device)
+            return WeightedRowSum(f.rows, f.index, f.weights, y, self._ones[:T])
+        return TensorSum(y, resolve(f))
 
     def prefetch_layer(self, layer: BuiltLayer, ctx: StepContext, caches) -> None:
         layer.mixer.prefetch_first(ctx, caches.get("mixer"))
