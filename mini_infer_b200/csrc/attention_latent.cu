@@ -4,7 +4,8 @@
 // position and common to all heads.  With the key matrices folded into the queries
 // (q'_h = W_uk,h^T q_h, so that q_h . (W_uk,h c) = q'_h . c) the attention itself is the engine's attention
 // over one shared key/value head whose keys are the cached rows and whose values are their first c numbers
-// (attention_mix.cu with a value row stride); what is left for this file:
+// (attention_mix.cu and attention_mix_tc.cu with a value row stride, attention_prefill_tc.cu with (query, head)
+// pairs as the rows of a query tile); what is left for this file:
 //
 //   latent_store   the cached row of every new token: unit-RMS latent times gain, rotated key part
 //   latent_query   the rotated part of every head's query into its place behind the folded part, and the

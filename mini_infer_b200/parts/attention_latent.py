@@ -10,9 +10,11 @@ Only ``[c | rot(k^rot)]`` is cached (``LatentNeed``).  The key matrices are fold
 ``q_h' = W_uk,h^T q_h^plain`` (so ``q_h^plain . W_uk,h c = q_h' . c``), and the value matrices are applied
 after the weighted sum (``sum_j p_j W_uv,h c_j = W_uv,h sum_j p_j c_j``): the attention itself then runs over
 one shared key/value head whose keys are the cached rows and whose values are their first ``kv_rank``
-numbers, with the engine's attention kernels (``ops.functional.attention_mix`` / ``attention_mix_tc``), for
-prompts and for decoding alike.  A layer may read the rows another layer caches (``shares_cache``): it then
-has no ``W_dkv`` of its own.
+numbers, with the engine's attention kernels, for prompts and for decoding alike: the float32 path takes
+``ops.functional.attention_mix`` for every step; the bfloat16 path takes ``attention_mix_tc`` (split over the
+keys) for decode steps and, for prompt portions, the tcgen05 kernel with (query, head) pairs as the rows of a
+query tile (``prefill_attention_tc_shared``) where the sizes allow, else ``attention_mix_tc``.  A layer may read
+the rows another layer caches (``shares_cache``): it then has no ``W_dkv`` of its own.
 
 The rotation pairs neighbouring dimensions (``2i`` with ``2i + 1``).
 """

@@ -4,9 +4,11 @@ Optionally every query and key head is first brought to unit root mean square an
 dimension.  ``score = (q . k) * scale``; ``score <- softcap * tanh(score / softcap)`` (if a cap is set); then every
 head's score of a (query, key) pair becomes a mix of all heads' scores of that pair,
 ``score_h <- sum_g talk[h, g] * score_g`` (if the layer has such a matrix); then the softmax over the keys a
-window lets through.  Query/key heads and value heads may differ in size.  One library product for q, k and
-v together, one kernel for rotation and cache write, one attention kernel that owns all heads of its
-queries (the mix couples them), one library product for the output.
+window lets through (behind a window the first keys of a request may stay visible).  Query/key heads and value
+heads may differ in size.  One library product for q, k and v together, one kernel for head norms, rotation and
+cache write, one attention kernel that owns all heads of its queries (the mix couples them), one library product
+for the output.  Without a mix and a cap the heads are independent: prompt portions in bfloat16 then take the
+engine's tcgen05 attention where keys and values have one size that kernel is built for.
 """
 
 from __future__ import annotations
