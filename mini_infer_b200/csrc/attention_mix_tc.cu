@@ -357,28 +357,37 @@ attn_mix_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
 }
 
-// out[b, h, :] from the partial results of the splits, in split order
+// out[b, h, :] from the partial results of the splits, in split order.  The splits' maxima and sums are fetched
+// once, all at a time, and every split's weight exp(m_s - m) is formed once for all columns.
+constexpr int kMergeMaxSplits = 12288;          // two floats a split in shared memory: 96 KiB
 __global__ void __launch_bounds__(128)
 attn_mix_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                       const int* __restrict__ q_start, __nv_bfloat16* __restrict__ out, int H, int DV, int splits) {
+    extern __shared__ float merge_sh[];         // [splits] weights, [splits] sums
+    float* wgt = merge_sh;
+    float* lsum = merge_sh + splits;
     wait_for_earlier_kernels();
     const int b = blockIdx.y, h = blockIdx.x;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(((size_t)b * splits + s) * H + h) * 2]);
-    float l = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const size_t base = ((size_t)b * splits + s) * H + h;
-        const float ms = part_ml[base * 2];
-        if (ms != -INFINITY) l += part_ml[base * 2 + 1] * expf(ms - m);
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
+        const float2 ml = *reinterpret_cast<const float2*>(part_ml + (((size_t)b * splits + s) * H + h) * 2);
+        wgt[s] = ml.x;
+        lsum[s] = ml.y;
     }
+    __syncthreads();
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, wgt[s]);
+    __syncthreads();
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) wgt[s] = wgt[s] == -INFINITY ? 0.f : expf(wgt[s] - m);
+    __syncthreads();
+    float l = 0.f;
+    for (int s = 0; s < splits; ++s) l += lsum[s] * wgt[s];        // in split order
     const float inv = l > 0.f ? 1.f / l : 0.f;
     const int row = q_start[b];
     for (int c = threadIdx.x; c < DV; c += blockDim.x) {
         float o = 0.f;
         for (int s = 0; s < splits; ++s) {
-            const size_t base = ((size_t)b * splits + s) * H + h;
-            const float ms = part_ml[base * 2];
-            if (ms != -INFINITY) o += part_o[base * DV + c] * expf(ms - m);
+            const float w = wgt[s];
+            if (w != 0.f) o += part_o[(((size_t)b * splits + s) * H + h) * DV + c] * w;
         }
         out[((size_t)row * H + h) * DV + c] = __float2bfloat16_rn(o * inv);
     }
@@ -434,7 +443,7 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
         set_last_error("mixed-head attention (tensor cores): heads %d/%d, key size %d, value size %d are not taken", H, G, dk, dv);
         return kBadShape;
     }
-    if (splits < 1 || (splits > 1 && (max_q_len != 1 || !part_o || !part_ml)) || B > 65535 || splits > 65535) {
+    if (splits < 1 || (splits > 1 && (max_q_len != 1 || !part_o || !part_ml)) || B > 65535 || splits > kMergeMaxSplits) {
         set_last_error("mixed-head attention (tensor cores): %d splits with portions of %d tokens, batch %d", splits, max_q_len, B);
         return kBadShape;
     }
@@ -459,7 +468,10 @@ int mi_attn_mix_tc(const void* q, const void* k_cache, const void* v_cache, cons
 #undef MI_TC_LAUNCH
     int launched = 1;
     if (splits > 1) {
-        launch_dependent(attn_mix_merge_kernel, dim3(H, B), dim3(128), 0, stream, (const float*)part_o,
+        const size_t merge_smem = (size_t)2 * splits * sizeof(float);
+        if (merge_smem > 48 * 1024)
+            cudaFuncSetAttribute(attn_mix_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem);
+        launch_dependent(attn_mix_merge_kernel, dim3(H, B), dim3(128), merge_smem, stream, (const float*)part_o,
                          (const float*)part_ml, q_start, (__nv_bfloat16*)out, H, dv, splits);
         launched = 2;
     }
