@@ -52,9 +52,25 @@ def _find_nvcc() -> str:
                        "and there is no fallback path")
 
 
-def _stamp() -> str:
+# the file that holds the library's shared state (last error, launch counter): part of every build
+CORE = ("elementwise.cu",)
+
+
+def _subset(only) -> Optional[List[str]]:
+    """The sources of a partial build (None: all of them): ``only`` plus the core, checked against the folder."""
+    if only is None:
+        return None
+    everything = sources()
+    unknown = sorted(set(only) - set(everything))
+    if unknown:
+        raise ValueError(f"mini_infer_b200: no CUDA source named {unknown}; there are {everything}")
+    chosen = sorted(set(only) | set(CORE))
+    return None if chosen == everything else chosen
+
+
+def _stamp(srcs: Optional[List[str]] = None) -> str:
     h = hashlib.sha256()
-    for f in sources() + _headers():
+    for f in (sources() if srcs is None else srcs) + _headers():
         h.update(f.encode())
         with open(os.path.join(HERE, f), "rb") as fh:
             h.update(fh.read())
@@ -96,19 +112,39 @@ def _compile_one(nvcc: str, src: str, obj: str, extra: List[str]) -> None:
         _say(p.stdout.strip())
 
 
-def build(verbose_ptxas: bool = False, force: bool = False) -> str:
-    """Build if needed and return the path of the shared library."""
-    bdir = _build_dir()
-    lib = os.path.join(bdir, LIB_NAME)
-    stamp_file = os.path.join(bdir, "stamp.txt")
-    stamp = _stamp()
-    if not force and os.path.exists(lib) and os.path.exists(stamp_file):
+def _paths(bdir: str, subset: Optional[List[str]]):
+    if subset is None:
+        return os.path.join(bdir, LIB_NAME), os.path.join(bdir, "stamp.txt")
+    tag = hashlib.sha256(" ".join(subset).encode()).hexdigest()[:10]
+    return os.path.join(bdir, LIB_NAME[:-3] + f"-{tag}.so"), os.path.join(bdir, f"stamp-{tag}.txt")
+
+
+def _current(lib: str, stamp_file: str, stamp: str) -> bool:
+    if os.path.exists(lib) and os.path.exists(stamp_file):
         with open(stamp_file) as f:
-            if f.read().strip() == stamp:
-                return lib
+            return f.read().strip() == stamp
+    return False
+
+
+def built_full() -> Optional[str]:
+    """The path of the whole library if it is built and current (no compile is started), else None."""
+    lib, stamp_file = _paths(_build_dir(), None)
+    return lib if _current(lib, stamp_file, _stamp()) else None
+
+
+def build(verbose_ptxas: bool = False, force: bool = False, only=None) -> str:
+    """Build if needed and return the path of the shared library.  ``only``: a partial library of these
+    sources (and the core), for a first call that should compile what one model needs and no more; it lies
+    beside the whole library under a name of its own."""
+    bdir = _build_dir()
+    subset = _subset(only)
+    lib, stamp_file = _paths(bdir, subset)
+    stamp = _stamp(subset)
+    if not force and _current(lib, stamp_file, stamp):
+        return lib
     nvcc = _find_nvcc()
-    srcs = sources()
-    _say(f"building {LIB_NAME} for sm_100a from {len(srcs)} CUDA files in {bdir} (first call only)")
+    srcs = sources() if subset is None else subset
+    _say(f"building {os.path.basename(lib)} for sm_100a from {len(srcs)} CUDA files in {bdir} (first call only)")
     done = threading.Event()
 
     def heartbeat():

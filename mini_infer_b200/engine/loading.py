@@ -14,7 +14,7 @@ from ..weights.random_init import RandomSource
 from .model import Model
 
 
-def _runtime(dtype: str, device) -> Runtime:
+def _runtime(dtype: str, device, kernel_files=None) -> Runtime:
     dev = torch.device(device)
     if dev.type != "cuda":
         raise RuntimeError(f"mini_infer_b200 runs on a CUDA device only (asked for '{device}'); "
@@ -26,7 +26,9 @@ def _runtime(dtype: str, device) -> Runtime:
     torch.cuda.set_device(dev)
     configure_matmul_exactness()
     from ..ops.library import library
-    library()  # build or load the kernels now: fail here, loudly, rather than in the first step
+    # build or load the kernels now: fail here, loudly, rather than in the first step (in a fresh checkout only
+    # the sources this model's parts name are compiled, plus the engine's own)
+    library(kernel_files)
     return Runtime(precision_from_name(dtype), dev)
 
 
@@ -42,8 +44,8 @@ def load_model(folder: str, dtype: str = "bfloat16", device="cuda:0") -> Tuple[M
     # sizes that only a tensor's shape gives: a builder may look them up here
     cj.setdefault("tensor_shapes", {n: tuple(source.shape(n)) for n in source.names()})
     spec = build_model_spec(cj)
-    rt = _runtime(dtype, device)
     model = Model(spec)
+    rt = _runtime(dtype, device, model.kernel_files())
     model.load(source, rt)
     return model, rt, cj
 
@@ -52,8 +54,8 @@ def random_model(config_json: Dict[str, Any], seed: int, dtype: str = "bfloat16"
                  spec=None) -> Tuple[Model, Runtime]:
     """A model with seeded random weights generated on the device (no folder is written)."""
     spec = spec or build_model_spec(config_json)
-    rt = _runtime(dtype, device)
     model = Model(spec)
+    rt = _runtime(dtype, device, model.kernel_files())
     src = RandomSource(model.tensor_decls(), seed, rt.act, str(rt.device))
     model.load(src, rt)
     return model, rt

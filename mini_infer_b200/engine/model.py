@@ -123,6 +123,18 @@ class Model:
         parts += [self.final_norm, self.lm_head]
         return parts
 
+    def kernel_files(self) -> List[str]:
+        """The CUDA sources whose kernels this model's parts may launch (parts inside parts included)."""
+        found, seen, todo = set(), set(), list(self.all_parts())
+        while todo:
+            part = todo.pop()
+            if id(part) in seen:
+                continue
+            seen.add(id(part))
+            found.update(getattr(part, "kernel_files", ()) or ())
+            todo.extend(v for v in vars(part).values() if isinstance(v, Part))
+        return sorted(found)
+
     def tensor_decls(self) -> List[TensorDecl]:
         out: List[TensorDecl] = []
         seen = set()

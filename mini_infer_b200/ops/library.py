@@ -11,7 +11,7 @@ import ctypes
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 from typing import Optional
 
-_lib: Optional[ctypes.CDLL] = None
+_lib: Optional["_Library"] = None
 _lib_path: Optional[str] = None
 
 P = c_void_p
@@ -67,71 +67,110 @@ _SIGNATURES = {
 }
 
 
-def library() -> ctypes.CDLL:
-    """The loaded library; built at the first call of a fresh checkout."""
+# entry points that are not launchers: name -> (argtypes, restype)
+_OTHERS = {
+    "mi_last_error": ([], c_char_p),
+    "mi_launch_count": ([], ctypes.c_longlong),
+    "mi_attn_decode_supported": ([I], c_int),
+    "mi_attn_prefill_supported": ([I], c_int),
+    "mi_grouped_gemm_tc_supported": ([I], c_int),
+    "mi_grouped_gemm_skinny_supported": ([I], c_int),
+    "mi_moe_route_small_max_tokens": ([], c_int),
+    "mi_moe_norm_route_small_max_width": ([], c_int),
+    "mi_set_dependent_launch": ([c_int], c_int),
+    "mi_moe_norm_route_small_takes": ([c_int, c_int, c_int, c_int], c_int),
+    "mi_grouped_gemm_skinny_pairs_split_inner_max_tokens": ([], c_int),
+    "mi_grouped_gemm_skinny_pairs_max_tokens": ([], c_int),
+    "mi_attn_prefill_tc_supported": ([I, I], c_int),
+    "mi_qkv_skinny_supported": ([I, I, I], c_int),
+    "mi_dense_skinny_max_rows": ([], c_int),
+    "mi_delta_scan_prep_row": ([I], c_int),
+    "mi_attn_mix_tc_supported": ([I, I, I, I], c_int),
+    "mi_attn_mix_tc_splits": ([I], c_int),
+    "mi_attn_mix_supported": ([I, I, I, I, I], c_int),
+    "mi_attn_prefill_tc_shared_supported": ([I, I, I, I], c_int),
+    "mi_attn_decode_split_size": ([], c_int),
+}
+
+# kernels that the engine itself calls, whatever the model: embedding, norms and the residual, the dense
+# products of both precision paths, weight prefetch, sampling, random weights
+ENGINE_SOURCES = ("elementwise.cu", "dense_f32.cu", "moe_skinny.cu", "prefetch.cu", "sampling.cu", "random_init.cu")
+
+
+class _Library:
+    """The entry points of one loaded library.  A partial library (built from the sources one model needs) lacks
+    the others' entry points: asking for one of those builds and loads the whole library in its place, so a
+    missing kernel costs a compile, never a wrong or a missing result."""
+
+    def __init__(self, cdll: ctypes.CDLL, path: str, sources):
+        self._cdll, self.path, self.sources = cdll, path, sources          # sources None: the whole library
+        for name, argtypes in _SIGNATURES.items():
+            self._bind(name, argtypes, c_int)
+        for name, (argtypes, restype) in _OTHERS.items():
+            self._bind(name, argtypes, restype)
+
+    def _bind(self, name, argtypes, restype) -> None:
+        try:
+            fn = getattr(self._cdll, name)
+        except AttributeError:
+            return
+        fn.argtypes = argtypes
+        fn.restype = restype
+        self.__dict__[name] = fn
+
+    def __getattr__(self, name):           # only reached for names that were not bound above
+        if name.startswith("_"):
+            raise AttributeError(name)
+        try:
+            return getattr(self._cdll, name)
+        except AttributeError:
+            if self.sources is None:
+                raise
+        return getattr(_load(None), name)
+
+
+_loaded: list = []       # every library this process loaded (a replaced one stays: captured graphs hold its kernels)
+
+
+def _load(needs) -> "_Library":
     global _lib, _lib_path
-    if _lib is not None:
-        return _lib
-    from ..csrc.build import build
-    path = build()
+    from ..csrc.build import CORE, build, built_full
+    path, sources = None, None
+    if needs is not None:
+        path = built_full()                 # the whole library is there already: nothing to compile
+        if path is None:
+            sources = frozenset(needs) | frozenset(CORE)
+            path = build(only=sorted(sources))
+    if path is None:
+        path = build()
     try:
-        lib = ctypes.CDLL(path)
+        cdll = ctypes.CDLL(path)
     except OSError as e:
         raise RuntimeError(f"mini_infer_b200: cannot load {path}: {e}") from e
-    for name, argtypes in _SIGNATURES.items():
-        fn = getattr(lib, name)
-        fn.argtypes = argtypes
-        fn.restype = c_int
-    lib.mi_last_error.restype = c_char_p
-    lib.mi_last_error.argtypes = []
-    lib.mi_launch_count.restype = ctypes.c_longlong
-    lib.mi_launch_count.argtypes = []
-    lib.mi_attn_decode_supported.argtypes = [I]
-    lib.mi_attn_decode_supported.restype = c_int
-    lib.mi_attn_prefill_supported.argtypes = [I]
-    lib.mi_attn_prefill_supported.restype = c_int
-    lib.mi_grouped_gemm_tc_supported.argtypes = [I]
-    lib.mi_grouped_gemm_tc_supported.restype = c_int
-    lib.mi_grouped_gemm_skinny_supported.argtypes = [I]
-    lib.mi_grouped_gemm_skinny_supported.restype = c_int
-    lib.mi_moe_route_small_max_tokens.argtypes = []
-    lib.mi_moe_route_small_max_tokens.restype = c_int
-    lib.mi_moe_norm_route_small_max_width.argtypes = []
-    lib.mi_moe_norm_route_small_max_width.restype = c_int
-    lib.mi_set_dependent_launch.argtypes = [c_int]
-    lib.mi_set_dependent_launch.restype = c_int
-    lib.mi_moe_norm_route_small_takes.argtypes = [c_int, c_int, c_int, c_int]
-    lib.mi_moe_norm_route_small_takes.restype = c_int
-    lib.mi_grouped_gemm_skinny_pairs_split_inner_max_tokens.argtypes = []
-    lib.mi_grouped_gemm_skinny_pairs_split_inner_max_tokens.restype = c_int
-    lib.mi_grouped_gemm_skinny_pairs_max_tokens.argtypes = []
-    lib.mi_grouped_gemm_skinny_pairs_max_tokens.restype = c_int
-    lib.mi_attn_prefill_tc_supported.argtypes = [I, I]
-    lib.mi_attn_prefill_tc_supported.restype = c_int
-    lib.mi_qkv_skinny_supported.argtypes = [I, I, I]
-    lib.mi_qkv_skinny_supported.restype = c_int
-    lib.mi_dense_skinny_max_rows.argtypes = []
-    lib.mi_dense_skinny_max_rows.restype = c_int
-    lib.mi_delta_scan_prep_row.argtypes = [I]
-    lib.mi_delta_scan_prep_row.restype = c_int
-    lib.mi_attn_mix_tc_supported.argtypes = [I, I, I, I]
-    lib.mi_attn_mix_tc_supported.restype = c_int
-    lib.mi_attn_mix_tc_splits.argtypes = [I]
-    lib.mi_attn_mix_tc_splits.restype = c_int
-    lib.mi_attn_mix_supported.argtypes = [I, I, I, I, I]
-    lib.mi_attn_mix_supported.restype = c_int
-    lib.mi_attn_prefill_tc_shared_supported.argtypes = [I, I, I, I]
-    lib.mi_attn_prefill_tc_shared_supported.restype = c_int
-    lib.mi_attn_decode_split_size.argtypes = []
-    lib.mi_attn_decode_split_size.restype = c_int
-    _lib = lib
-    _lib_path = path
+    lib = _Library(cdll, path, sources)
+    if "mi_last_error" not in lib.__dict__:
+        raise RuntimeError(f"mini_infer_b200: {path} lacks the library's core entry points")
+    _loaded.append(lib)
+    _lib, _lib_path = lib, path
     return lib
+
+
+def library(needs=None) -> "_Library":
+    """The loaded library; built at the first call of a fresh checkout.  ``needs`` (names of CUDA sources): what
+    the caller is going to use; when nothing is built yet, only those (and the engine's own) are compiled.  A
+    call without ``needs`` takes whatever is loaded."""
+    if _lib is not None:
+        if needs is None or _lib.sources is None or set(needs) <= _lib.sources:
+            return _lib
+    if needs is not None:
+        needs = set(needs) | set(ENGINE_SOURCES)
+    return _load(needs)
 
 
 def launch_count() -> int:
     """Kernels of this library queued so far in this process."""
-    return int(library().mi_launch_count())
+    library()
+    return sum(int(lib.mi_launch_count()) for lib in _loaded)
 
 
 def library_path() -> Optional[str]:

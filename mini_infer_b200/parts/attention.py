@@ -32,6 +32,7 @@ class GQAttention(Mixer):
     """
 
     graph_safe = True
+    kernel_files = ("attention.cu", "attention_prefill.cu", "attention_prefill_tc.cu", "elementwise.cu", "moe_skinny.cu")
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)

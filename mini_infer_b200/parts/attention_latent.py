@@ -42,6 +42,8 @@ class LatentAttention(Mixer):
     ``uv [heads*value_dim, kv_rank]``, ``g [heads*value_dim, hidden]``, ``o [hidden, heads*value_dim]``."""
 
     graph_safe = True
+    kernel_files = ("attention_latent.cu", "attention_mix.cu", "attention_mix_tc.cu", "attention_prefill_tc.cu",
+                    "dense_f32.cu", "elementwise.cu")
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)

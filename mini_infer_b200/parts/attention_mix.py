@@ -38,6 +38,7 @@ class HeadMixAttention(Mixer):
     ``qk_norm``."""
 
     graph_safe = True
+    kernel_files = ("attention_mix.cu", "attention_mix_tc.cu", "attention_prefill_tc.cu")
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)

@@ -206,6 +206,10 @@ class StepContext:
 
 class Part:
     category = ""
+    # the CUDA sources (names in csrc/) whose kernels this part may launch: a first call in a fresh checkout
+    # compiles the sources of the model's parts and the engine's own, not the whole library.  A part that
+    # leaves one out still works (asking for a missing entry point builds the whole library in its place).
+    kernel_files: Tuple[str, ...] = ()
 
     def __init__(self, params: Mapping[str, Any], prefix: str):
         self.params = dict(params)

@@ -193,6 +193,7 @@ class StreamMerge(Block):
     graph_safe = True
     accepts_deferred = True
     needs_embedding_output = True
+    kernel_files = ("residual_forms.cu",)
     roles: dict = {}
 
     def tensor_decls(self) -> List[TensorDecl]:

@@ -29,6 +29,7 @@ class SwiGLUMLP(FeedForward):
     """
 
     graph_safe = True
+    kernel_files = ("elementwise.cu", "moe_skinny.cu")
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -64,6 +65,7 @@ class GatedMLP(FeedForward):
     Tensors: ``<prefix><gate>, <prefix><up> [I, H]``, ``<prefix><down> [H, I]``."""
 
     graph_safe = True
+    kernel_files = ("elementwise.cu", "moe_skinny.cu", "residual_forms.cu")
     ACTIVATIONS = ("silu", "gelu_tanh", "clamped_swish")
 
     def __init__(self, params, prefix):
@@ -120,6 +122,7 @@ class SparseMoE(FeedForward):
     """
 
     graph_safe = True
+    kernel_files = ("moe.cu", "moe_skinny.cu", "moe_tc.cu", "elementwise.cu")
     # which kernel a step of a given size takes, and where the shared expert is forked, are measured
     # thresholds: parts/tuning.py
 

@@ -23,6 +23,7 @@ class RMSNorm(Norm):
 
     graph_safe = True
     accepts_deferred = True
+    kernel_files = ("elementwise.cu",)
 
     def _name(self) -> str:
         return self.prefix + self.params.get("tensor", "weight")
@@ -59,6 +60,7 @@ class ScalarRMSNorm(Norm):
 
     graph_safe = True
     accepts_deferred = True
+    kernel_files = ("residual_forms.cu",)
 
     def _name(self) -> str:
         return self.prefix + self.params.get("tensor", "weight")

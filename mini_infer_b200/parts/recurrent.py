@@ -44,6 +44,7 @@ class ChannelGatedDelta(Mixer):
     ``o [hidden, heads*value_dim]``."""
 
     graph_safe = True
+    kernel_files = ("recurrent.cu",)
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
@@ -123,6 +124,7 @@ class Mamba2(Mixer):
     ``norm [inner]``, ``o [hidden, inner]``; ``inner = heads * head_dim``."""
 
     graph_safe = True
+    kernel_files = ("recurrent.cu",)
 
     def __init__(self, params, prefix):
         super().__init__(params, prefix)

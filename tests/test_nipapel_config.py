@@ -144,3 +144,21 @@ def test_plain_router_weights_are_the_softmax_over_the_chosen_logits():
     rec = []
     pn.routed_ff(h, w, "l1.mlp.", cfg["layers"][1]["mlp"], chosen=rec)
     assert bool((rec[0][0] == 2).any(dim=1).all())
+
+
+def test_a_model_names_the_kernel_sources_it_needs():
+    """What a first call in a fresh checkout compiles: the sources of the model's parts and the engine's own."""
+    from mini_infer_b200.config import build_model_spec
+    from mini_infer_b200.csrc import build as B
+    from mini_infer_b200.engine.model import Model
+    from mini_infer_b200.ops.library import ENGINE_SOURCES
+    files = set(Model(build_model_spec(nt.CONFIG_A)).kernel_files())
+    assert {"attention_latent.cu", "attention_mix.cu", "attention_prefill_tc.cu", "moe.cu", "residual_forms.cu"} <= files
+    assert not files & {"recurrent.cu", "attention.cu", "attention_prefill.cu"}
+    assert files | set(ENGINE_SOURCES) <= set(B.sources())
+    # a partial build always holds the core; all sources together are the whole library; unknown names are refused
+    assert B._subset(["moe.cu"]) == sorted({"moe.cu", *B.CORE})
+    assert B._subset(B.sources()) is None and B._subset(None) is None
+    with pytest.raises(ValueError):
+        B._subset(["no_such_kernels.cu"])
+    assert B._paths("/x", None)[0] != B._paths("/x", ["elementwise.cu", "moe.cu"])[0]
